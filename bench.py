@@ -1,0 +1,372 @@
+"""Benchmark of the DLR-Net forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward of the whole L-layer stack over one batch of M
+synthetic token rows.  The default workload is the shape the headline metric
+is quoted on: d=4096, r=128, L=143 (kernels/reference.py:18-23, "Qwen3-8B"),
+M=8192 rows per GPU, bf16, seeded N(0,1) inputs and the reference's
+initialisation scales with alpha=0.01 (kernels/reference.py:46-55).  With N
+GPUs every rank runs the same number of rows on its own replica of the weights
+(rows are independent, so there is no collective in the timed region) and the
+reported value is the total rows per second, timed on the device and taken as
+the maximum over ranks.
+
+The single JSON line also carries: the tensor-core roofline of the large-batch
+kernel, the same forward measured through the host-buffer C-ABI entry point
+(``e2e``), the small-batch (decode) latencies with their weight-streaming
+bandwidth, the clocks sampled during the run, and a CPU baseline (the oracle's
+restatement of the reference's torch loop, timed on this machine's cores).
+
+``--impl reference`` times that CPU restatement alone, on bounded samples of the
+same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [ROOT, os.path.join(ROOT, "ml-dlr-lock_b200")]
+
+import torch  # noqa: E402
+
+METRIC = "DLR-Net fwd tokens/s at d=4096 r=128 L=143 (M=1..8192); % HBM/TC roofline"
+WORKLOADS = {
+    # name: d, d_ff, r, L, seed  (BASELINE configs 1-4)
+    "cfg1": (1024, 3072, 32, 141, 0),
+    "cfg2": (2048, 6144, 64, 142, 1),
+    "cfg3": (4096, 12288, 128, 143, 2),
+    "cfg4": (5120, 25600, 256, 149, 3),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], tf_burst=p["bf16_tflops"], tf_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+# --------------------------------------------------------------------------- #
+# clocks
+# --------------------------------------------------------------------------- #
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the bench runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake"}
+
+    def __init__(self, device: int):
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._mark = None
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self._nv = pynvml
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # pragma: no cover - depends on the box
+            self._nv = None
+            self.error = repr(e)
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                self.samples.append((time.perf_counter(), mhz, mask))
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def mark(self):
+        self._mark = time.perf_counter()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+        end = time.perf_counter()
+        inside = [s for s in self.samples if self._mark is not None and self._mark <= s[0] <= end]
+        use = inside or self.samples
+        reasons = set()
+        for _, _, mask in use:
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median([s[1] for s in use]) if use else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(reasons), "samples": len(use)}
+
+
+# --------------------------------------------------------------------------- #
+# synthetic problem
+# --------------------------------------------------------------------------- #
+def make_weights(d, r, L, seed, device, alpha=0.01):
+    """Folded bf16 weights with the reference's initialisation scales
+    (dlr_lock/model.py:65-68): V ~ N(0, 1/d), U ~ N(0, 1/(rL)), gain 1."""
+    from dlr_lock_b200 import ops
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    V = torch.randn(L, r, d, device=device, generator=g) * (1.0 / math.sqrt(d))
+    U = torch.randn(L, d, r, device=device, generator=g) * (1.0 / math.sqrt(r * L))
+    gain = torch.ones(L, d, device=device)
+    a = torch.full((L,), alpha, device=device)
+    Vp, Up = ops.fold_weights(V, U, gain, a)
+    del V, U
+    return Vp, Up
+
+
+def time_steps(fn, steps, warmup, dist_barrier=None):
+    """Device time of `steps` calls after `warmup`, ms total."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist_barrier:
+        dist_barrier()
+    torch.cuda.synchronize()
+    a = torch.cuda.Event(enable_timing=True)
+    b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    if dist_barrier:
+        dist_barrier()
+    return a.elapsed_time(b)
+
+
+def min_latency_us(fn, iters=200, warmup=20):
+    """Minimum single-call device time (kernels/bench/_protocol.py:83-105 form)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    best = float("inf")
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = [a.elapsed_time(b) * 1e3 for a, b in evs]
+    return min(ts), statistics.median(ts)
+
+
+# --------------------------------------------------------------------------- #
+# CPU baseline (oracle port of the reference's torch loop)
+# --------------------------------------------------------------------------- #
+def cpu_forward_sampler(d, r, L, seed, rows):
+    from oracle import dlrnet_oracle as O
+    p, x = O.seeded_case(d, r, L, rows, seed, alpha=0.01)
+    return lambda: O.forward_eager(x, p)
+
+
+def cpu_baseline(d, r, L, seed, rows=512, budget_s=12.0):
+    fn = cpu_forward_sampler(d, r, L, seed, rows)
+    fn()
+    best, spent, reps = float("inf"), 0.0, 0
+    while spent < budget_s and reps < 8:
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        best = min(best, dt)
+        spent += dt
+        reps += 1
+    return {"value": rows / best, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{rows} rows of the same d/r/L, bf16 torch CPU loop (oracle.forward_eager), best of {reps}"}
+
+
+def run_reference_arm(args, d, r, L, seed):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 256
+    fn = cpu_forward_sampler(d, r, L, seed, rows)
+    for _ in range(min(args.warmup, 2)):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = time.perf_counter() - t0
+    v = rows * args.steps / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 2), "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: d={d} r={r} L={L}, {rows}-row sample per step on host cores"},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{rows} rows per step, bf16 torch CPU loop (oracle.forward_eager)"},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- #
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--rows", type=int, default=8192, help="token rows per GPU per step")
+    ap.add_argument("--no-extras", action="store_true", help="skip decode sweep, e2e and CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    d, d_ff, r, L, seed = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, d, r, L, seed)
+        return
+
+    from dlr_lock_b200 import ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    barrier = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        barrier = dist.barrier
+    ops._lib.load()
+    peaks = measured_peaks()
+
+    M = args.rows
+    Vp, Up = make_weights(d, r, L, seed, dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(1000 + seed + rank)
+    xs = [torch.randn(M, d, device=dev, generator=g).to(torch.bfloat16) for _ in range(2)]
+    ys = [torch.empty_like(x) for x in xs]
+    plan = ops.query(M, d, r, L)
+    it = [0]
+
+    def step():
+        i = it[0] & 1
+        it[0] += 1
+        ops.forward_folded(xs[i], Vp, Up, out=ys[i])
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    ops.check_status()
+    sampler.mark()
+    ms = time_steps(step, args.steps, args.warmup, barrier)
+    clocks = sampler.stop()
+    ops.check_status()
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    value = world * M * 1e3 / ms_step
+
+    flops = 4.0 * L * M * d * r
+    launches_per_step = plan.passes
+    kernel_ms = ms_step / launches_per_step
+    timed_s = ms / 1e3
+    peak_tf = peaks["tf_sustained"] if timed_s > 1.0 else peaks["tf_burst"]
+    achieved_tf = flops / launches_per_step / (kernel_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
+                "frac": achieved_tf / peak_tf, "traffic": None,
+                "peak_source": f"{peaks['source']} ({'sustained' if timed_s > 1.0 else 'burst'})",
+                "kernel": "cluster" if plan.path == 2 else "striped", "kernel_ms": kernel_ms,
+                "frac_of_nominal_2250": achieved_tf / 2250.0}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: DLR-Net forward d={d} r={r} L={L}, M={M} rows per GPU, alpha=0.01",
+                   "rows_per_gpu": M, "l2": "inputs exceed L2 (weights %.0f MB + two alternating %d MB batches)"
+                   % (4.0 * L * d * r / 1e6, M * d * 2 // 1000000),
+                   "parallelism": f"rows x{world}, weights replicated"},
+        "roofline": roofline, "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
+        "plan": {"path": plan.path, "grid": plan.grid, "cluster": plan.cluster, "stripe_cols": plan.stripe_cols,
+                 "passes": plan.passes},
+    }
+
+    # ---- end to end through the host-buffer entry point (every rank, max over ranks)
+    if not args.no_extras:
+        xh = [x.cpu().pin_memory() for x in xs]
+        yh = [torch.empty_like(x).pin_memory() for x in xh]
+        jt = [0]
+
+        def step_host():
+            i = jt[0] & 1
+            jt[0] += 1
+            ops.forward_host(xh[i], yh[i], xs[i], ys[i], Vp, Up)
+
+        ms_h = time_steps(step_host, args.steps, 3, barrier)
+        if world > 1:
+            t = torch.tensor([ms_h], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_h = float(t.item())
+        line["e2e"] = {"value": world * M * args.steps * 1e3 / ms_h, "unit": "tokens/s",
+                       "h2d_bytes_per_step": M * d * 2, "d2h_bytes_per_step": M * d * 2,
+                       "ms_per_step": ms_h / args.steps}
+        ops.check_status()
+
+    # ---- small-batch latencies and other prefill sizes (rank 0, N=1 only)
+    if not args.no_extras and world == 1:
+        wbytes = 4.0 * L * d * r
+        dec = []
+        for m in (1, 4, 16, 64):
+            xm, ym = xs[0][:m].contiguous(), torch.empty(m, d, device=dev, dtype=torch.bfloat16)
+            lo, med = min_latency_us(lambda: ops.forward_folded(xm, Vp, Up, out=ym))
+            gbs = (wbytes + 4.0 * m * d) / (lo * 1e-6) / 1e9
+            dec.append({"M": m, "min_us": lo, "median_us": med, "us_per_layer": lo / L, "algorithmic_GBps": gbs,
+                        "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "tokens_per_s": m / (lo * 1e-6)})
+        line["decode"] = dec
+        pre = []
+        for m in (1024, 4096):
+            if m >= M:
+                continue
+            xm, ym = xs[0][:m].contiguous(), torch.empty(m, d, device=dev, dtype=torch.bfloat16)
+            lo, med = min_latency_us(lambda: ops.forward_folded(xm, Vp, Up, out=ym), iters=10, warmup=3)
+            pre.append({"M": m, "min_us": lo, "tokens_per_s": m / (lo * 1e-6),
+                        "TFLOPs": 4.0 * L * m * d * r / (lo * 1e-6) / 1e12})
+        line["prefill_other"] = pre
+        ops.check_status()
+        line["cpu_baseline"] = cpu_baseline(d, r, L, seed)
+
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

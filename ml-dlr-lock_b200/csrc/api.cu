@@ -1,0 +1,331 @@
+// C-ABI layer: argument checks, path selection, tensor-map encoding, launches.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "cluster.h"
+#include "decode.h"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+inline bool cuda_ok(cudaError_t e) {
+    if (e != cudaSuccess) {
+        g_last_cuda_error = int(e);
+        (void)cudaGetLastError();
+        return false;
+    }
+    return true;
+}
+
+struct DevInfo {
+    int num_sms = 0;
+    int smem_optin = 0;
+    int cc_major = 0;
+    bool ok = false;
+};
+
+DevInfo g_dev[64];
+std::mutex g_dev_mutex;
+
+// Device facts are cached per device index; the only process-wide state.
+int device_info(DevInfo* out) {
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev))) return DLRB200_ERR_CUDA;
+    if (dev < 0 || dev >= 64) return DLRB200_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DevInfo& d = g_dev[dev];
+    if (!d.ok) {
+        if (!cuda_ok(cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev)) ||
+            !cuda_ok(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) ||
+            !cuda_ok(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev)))
+            return DLRB200_ERR_CUDA;
+        d.ok = true;
+    }
+    *out = d;
+    return DLRB200_OK;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static std::atomic<EncodeTiledFn> cached{nullptr};
+    EncodeTiledFn f = cached.load(std::memory_order_acquire);
+    if (f) return f;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (!cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q)) ||
+        q != cudaDriverEntryPointSuccess || !p)
+        return nullptr;
+    f = reinterpret_cast<EncodeTiledFn>(p);
+    cached.store(f, std::memory_order_release);
+    return f;
+}
+
+int env_int(const char* name, int dflt) {
+    const char* v = std::getenv(name);
+    return (v && *v) ? std::atoi(v) : dflt;
+}
+
+bool supported_rank(int r) { return r == 16 || r == 32 || r == 64 || r == 128 || r == 256; }
+
+// Stripe width of the small-batch path: the narrowest of 16/32/64 columns whose
+// stripe count fits one CTA per SM (all CTAs must be co-resident).
+int pick_stripe_cols(int d, int num_sms) {
+    const int forced = env_int("DLRB200_STRIPE_COLS", 0);
+    if (forced == 16 || forced == 32 || forced == 64) return (d % forced == 0) ? forced : 0;
+    for (int dc : {16, 32, 64})
+        if (d % dc == 0 && d / dc <= num_sms) return dc;
+    return 0;
+}
+
+constexpr size_t kCtrlBytes = 256;
+
+size_t striped_workspace_bytes(int r) { return kCtrlBytes + dlr::decode_zacc_floats(r) * sizeof(float); }
+
+unsigned int spin_limit() { return unsigned(env_int("DLRB200_SPIN_LIMIT", 1 << 21)); }
+
+int striped_forward(const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r, int L,
+                    float eps, void* workspace, int* status_dev, cudaStream_t stream, const DevInfo& di) {
+    const int dc = pick_stripe_cols(d, di.num_sms);
+    if (dc == 0) return DLRB200_ERR_UNSUPPORTED_SHAPE;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return DLRB200_ERR_CUDA;
+
+    dlr::DecodeLaunch a;
+    std::memset(&a, 0, sizeof(a));
+    int vbc, vbr, ubc, ubr, vsw, usw;
+    if (!dlr::decode_box_dims(r, dc, &vbc, &vbr, &ubc, &ubr, &vsw, &usw)) return DLRB200_ERR_UNSUPPORTED_SHAPE;
+    if (!dlr::encode_2d_bf16(reinterpret_cast<void*>(enc), &a.tmV, Vp, uint64_t(d), uint64_t(L) * r, vbc, vbr, vsw) ||
+        !dlr::encode_2d_bf16(reinterpret_cast<void*>(enc), &a.tmU, Up, uint64_t(r), uint64_t(L) * d, ubc, ubr, usw)) {
+        g_last_cuda_error = -1;
+        return DLRB200_ERR_CUDA;
+    }
+    a.d = d; a.r = r; a.L = L; a.dc = dc;
+    a.num_sms = di.num_sms;
+    a.smem_optin = di.smem_optin;
+    a.max_stages = env_int("DLRB200_MAX_STAGES", 0);
+    a.stream = stream;
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    a.p.d = d; a.p.L = L; a.p.eps = eps; a.p.inv_d = 1.0f / float(d);
+    a.p.counter = reinterpret_cast<unsigned int*>(ws);
+    a.p.zacc = reinterpret_cast<float*>(ws + kCtrlBytes);
+    a.p.status = status_dev;
+    a.p.spin_limit = spin_limit();
+
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* yb = static_cast<__nv_bfloat16*>(y);
+    for (int row0 = 0; row0 < M; row0 += 64) {
+        const int rows = (M - row0 < 64) ? (M - row0) : 64;
+        const int mp = rows <= 8 ? 8 : (rows <= 16 ? 16 : (rows <= 32 ? 32 : 64));
+        const size_t clear = kCtrlBytes + size_t(3) * mp * (r + 4) * sizeof(float);
+        if (!cuda_ok(cudaMemsetAsync(ws, 0, clear, stream))) return DLRB200_ERR_CUDA;
+        a.p.x = xb + size_t(row0) * d;
+        a.p.y = yb + size_t(row0) * d;
+        a.p.M = rows;
+        const int rc = dlr::decode_launch(a);
+        if (rc != DLRB200_OK) {
+            if (rc == DLRB200_ERR_CUDA) g_last_cuda_error = int(cudaGetLastError());
+            return rc;
+        }
+    }
+    return DLRB200_OK;
+}
+
+__global__ void fold_v_kernel(const __nv_bfloat16* __restrict__ V, const __nv_bfloat16* __restrict__ gain,
+                              __nv_bfloat16* __restrict__ Vp, int d, int r, size_t total) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t layer = i / (size_t(r) * d);
+    const int col = int(i % d);
+    Vp[i] = __float2bfloat16_rn(__bfloat162float(V[i]) * __bfloat162float(gain[layer * d + col]));
+}
+
+__global__ void fold_u_kernel(const __nv_bfloat16* __restrict__ U, const float* __restrict__ alpha,
+                              __nv_bfloat16* __restrict__ Up, int d, int r, size_t total) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t layer = i / (size_t(r) * d);
+    Up[i] = __float2bfloat16_rn(__bfloat162float(U[i]) * alpha[layer]);
+}
+
+__global__ void transpose_stack_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                       int rows, int cols) {
+    __shared__ __nv_bfloat16 tile[32][33];
+    const size_t base = size_t(blockIdx.z) * rows * cols;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int rr = r0 + j, cc = c0 + threadIdx.x;
+        if (rr < rows && cc < cols) tile[j][threadIdx.x] = src[base + size_t(rr) * cols + cc];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int cc = c0 + j, rr = r0 + threadIdx.x;
+        if (rr < rows && cc < cols) dst[base + size_t(cc) * rows + rr] = tile[threadIdx.x][j];
+    }
+}
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+int check_shape(int M, int d, int r, int L) {
+    if (M < 0 || d <= 0 || r <= 0 || L <= 0) return DLRB200_ERR_INVALID_ARG;
+    if (d % 16 != 0 || !supported_rank(r)) return DLRB200_ERR_UNSUPPORTED_SHAPE;
+    return DLRB200_OK;
+}
+
+// Which path serves M rows.  The cluster path handles any M in 128-row tiles
+// once a tile's worth of rows makes the tensor-memory path pay off.
+bool use_cluster_path(int M, int d, int r, int L) {
+    const int forced = env_int("DLRB200_FORCE_PATH", 0);
+    if (forced == DLRB200_PATH_STRIPED) return false;
+    if (!dlr::cluster_supported(d, r, L)) return false;
+    if (forced == DLRB200_PATH_CLUSTER) return true;
+    return M > 64;
+}
+
+}  // namespace
+
+namespace dlr {
+
+bool encode_2d_bf16(void* encode_fn_ptr, CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+                    int box_inner, int box_outer, int swizzle_bytes) {
+    EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(encode_fn_ptr);
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * 2};
+    cuuint32_t box[2] = {cuuint32_t(box_inner), cuuint32_t(box_outer)};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+    if (swizzle_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
+    else if (swizzle_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
+    else if (swizzle_bytes == 128) sw = CU_TENSOR_MAP_SWIZZLE_128B;
+    else return false;
+    const CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
+}  // namespace dlr
+
+extern "C" {
+
+int dlrb200_version(void) { return 100; }
+
+const char* dlrb200_strerror(int code) {
+    switch (code & 0xff) {
+        case DLRB200_OK: return "ok";
+        case DLRB200_ERR_INVALID_ARG: return "invalid argument (null pointer or non-positive size)";
+        case DLRB200_ERR_UNSUPPORTED_SHAPE: return "unsupported shape (d must be a multiple of 16, r one of 16/32/64/128/256, and the stripes must fit the device)";
+        case DLRB200_ERR_ALIGNMENT: return "misaligned buffer (activations and weights need 16-byte, the workspace 256-byte alignment)";
+        case DLRB200_ERR_WORKSPACE: return "workspace too small";
+        case DLRB200_ERR_OCCUPANCY: return "the grid cannot be made co-resident on this device";
+        case DLRB200_ERR_CUDA: return "CUDA runtime or driver error (see dlrb200_last_cuda_error)";
+        case DLRB200_ERR_TIMEOUT_BARRIER: return "device-side wait on the per-layer exchange gave up";
+        case DLRB200_ERR_TIMEOUT_COPY: return "device-side wait on a weight copy gave up";
+    }
+    return "unknown error";
+}
+
+int dlrb200_last_cuda_error(void) { return g_last_cuda_error; }
+
+size_t dlrb200_workspace_bytes(int M, int d, int r, int L) {
+    if (check_shape(M, d, r, L) != DLRB200_OK) return 0;
+    size_t need = striped_workspace_bytes(r);
+    const size_t c = dlr::cluster_workspace_bytes(M, d, r, L);
+    if (c > need) need = c;
+    return (need + 255) & ~size_t(255);
+}
+
+int dlrb200_query(int M, int d, int r, int L, dlrb200_plan* plan) {
+    if (!plan) return DLRB200_ERR_INVALID_ARG;
+    int rc = check_shape(M, d, r, L);
+    if (rc != DLRB200_OK) return rc;
+    DevInfo di;
+    rc = device_info(&di);
+    if (rc != DLRB200_OK) return rc;
+    std::memset(plan, 0, sizeof(*plan));
+    plan->workspace_bytes = dlrb200_workspace_bytes(M, d, r, L);
+    if (use_cluster_path(M, d, r, L)) return dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
+    const int dc = pick_stripe_cols(d, di.num_sms);
+    if (dc == 0) return DLRB200_ERR_UNSUPPORTED_SHAPE;
+    plan->path = DLRB200_PATH_STRIPED;
+    plan->grid = d / dc;
+    plan->cluster = 1;
+    plan->stripe_cols = dc;
+    plan->rows_per_pass = M < 64 ? M : 64;
+    plan->passes = (M + 63) / 64;
+    return DLRB200_OK;
+}
+
+int dlrb200_forward(const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r, int L,
+                    float eps, void* workspace, size_t workspace_bytes, int* status_dev, void* stream) {
+    int rc = check_shape(M, d, r, L);
+    if (rc != DLRB200_OK) return rc;
+    if (M == 0) return DLRB200_OK;
+    if (!x || !y || !Vp || !Up || !workspace || !status_dev || x == y) return DLRB200_ERR_INVALID_ARG;
+    if (!aligned(x, 16) || !aligned(y, 16) || !aligned(Vp, 16) || !aligned(Up, 16) || !aligned(workspace, 256) ||
+        !aligned(status_dev, 4))
+        return DLRB200_ERR_ALIGNMENT;
+    if (workspace_bytes < dlrb200_workspace_bytes(M, d, r, L)) return DLRB200_ERR_WORKSPACE;
+    DevInfo di;
+    rc = device_info(&di);
+    if (rc != DLRB200_OK) return rc;
+    if (di.cc_major != 10) return DLRB200_ERR_CUDA;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (use_cluster_path(M, d, r, L)) {
+        EncodeTiledFn enc = encode_fn();
+        if (!enc) return DLRB200_ERR_CUDA;
+        rc = dlr::cluster_forward(reinterpret_cast<void*>(enc), x, y, Vp, Up, M, d, r, L, eps, workspace, status_dev,
+                                  st, di.num_sms, di.smem_optin, spin_limit());
+        if (rc == DLRB200_ERR_CUDA) g_last_cuda_error = int(cudaGetLastError());
+        return rc;
+    }
+    return striped_forward(x, y, Vp, Up, M, d, r, L, eps, workspace, status_dev, st, di);
+}
+
+int dlrb200_forward_host(const void* x_host, void* y_host, void* x_dev, void* y_dev, const void* Vp,
+                         const void* Up, int M, int d, int r, int L, float eps, void* workspace,
+                         size_t workspace_bytes, int* status_dev, void* stream) {
+    if (!x_host || !y_host) return DLRB200_ERR_INVALID_ARG;
+    if (M <= 0 || d <= 0) return M == 0 ? DLRB200_OK : DLRB200_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t bytes = size_t(M) * d * 2;
+    if (!x_dev || !y_dev) return DLRB200_ERR_INVALID_ARG;
+    if (!cuda_ok(cudaMemcpyAsync(x_dev, x_host, bytes, cudaMemcpyHostToDevice, st))) return DLRB200_ERR_CUDA;
+    const int rc = dlrb200_forward(x_dev, y_dev, Vp, Up, M, d, r, L, eps, workspace, workspace_bytes, status_dev,
+                                   stream);
+    if (rc != DLRB200_OK) return rc;
+    if (!cuda_ok(cudaMemcpyAsync(y_host, y_dev, bytes, cudaMemcpyDeviceToHost, st))) return DLRB200_ERR_CUDA;
+    return DLRB200_OK;
+}
+
+int dlrb200_fold_weights(const void* V, const void* U, const void* gain, const float* alpha, void* Vp,
+                         void* Up, int d, int r, int L, void* stream) {
+    if (!V || !U || !gain || !alpha || !Vp || !Up || d <= 0 || r <= 0 || L <= 0) return DLRB200_ERR_INVALID_ARG;
+    const size_t total = size_t(L) * r * d;
+    const int threads = 256;
+    const unsigned blocks = unsigned((total + threads - 1) / threads);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    fold_v_kernel<<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(V),
+                                              static_cast<const __nv_bfloat16*>(gain),
+                                              static_cast<__nv_bfloat16*>(Vp), d, r, total);
+    fold_u_kernel<<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(U), alpha,
+                                              static_cast<__nv_bfloat16*>(Up), d, r, total);
+    return cuda_ok(cudaGetLastError()) ? DLRB200_OK : DLRB200_ERR_CUDA;
+}
+
+int dlrb200_transpose_stack(const void* src, void* dst, int L, int rows, int cols, void* stream) {
+    if (!src || !dst || L <= 0 || rows <= 0 || cols <= 0 || src == dst) return DLRB200_ERR_INVALID_ARG;
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32, L), block(32, 8);
+    transpose_stack_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), rows, cols);
+    return cuda_ok(cudaGetLastError()) ? DLRB200_OK : DLRB200_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,214 @@
+"""CPU oracle for the DLR-Net forward pass.  TEST INFRASTRUCTURE ONLY.
+
+This file restates, on the CPU, the arithmetic that the reference performs in
+``dlr_lock/model.py:93-101`` (the L-layer residual loop), the parameter
+initialisation of ``dlr_lock/model.py:58-81``, the depth rule of
+``dlr_lock/model.py:130-139`` and the weight folding of
+``kernels/reference.py:68-91``.  It exists so that the CUDA path can be
+checked on a machine where the reference checkout is not present.  Nothing in
+the shipped package imports it: only the tests, the smoke entry and the
+``cpu_baseline`` / ``--impl reference`` legs of the benchmark do, and only as
+the checker or the timed CPU baseline, never as a compute fallback.
+
+Parity pin: every function here is compared against outputs of the real
+reference (imported from its checkout when the fixtures were generated) that
+are stored under ``tests/golden/``; see ``tests/golden/make_golden.py`` and
+``tests/test_oracle_golden.py``.
+
+Two oracles are defined, both on identical bf16-rounded weights and inputs:
+
+* ``forward_eager``  - every op runs in the parameter dtype exactly in the
+  order the reference module issues them, so with bf16 parameters each
+  intermediate is re-rounded to bf16 (the reference's own bf16 forward).
+* ``forward_fp32``   - the same loop with all tensors widened to fp32 first
+  ("identical bf16 weights, fp32 accumulate").
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+EPS = 1e-6  # dlr_lock/model.py:58 default; kernels/reference.py:26
+
+
+# --------------------------------------------------------------------------- #
+# Shapes
+# --------------------------------------------------------------------------- #
+def depth_for_budget(d: int, d_ff: int, r: int, multiplier: float = 1.0) -> int:
+    """Depth whose parameter count fits ``multiplier`` x a SwiGLU MLP.
+
+    Follows dlr_lock/model.py:130-139: budget 3*d*d_ff, cost per layer
+    2*d*r + d + 1, floor division, never below 2.
+    """
+    budget = int(3 * d * d_ff * multiplier)
+    return max(budget // (2 * d * r + d + 1), 2)
+
+
+def param_count(d: int, r: int, depth: int) -> int:
+    """dlr_lock/model.py:125-127."""
+    return depth * (2 * d * r + d + 1)
+
+
+# The four shapes the reference benchmarks (kernels/reference.py:18-23) and the
+# depths its smoke test pins (examples/smoke_test.py:90-95).
+SHAPES = {
+    "Qwen3-0.6B": dict(d=1024, d_ff=3072, r=32, L=141),
+    "Qwen3-1.7B": dict(d=2048, d_ff=6144, r=64, L=142),
+    "Qwen3-8B": dict(d=4096, d_ff=12288, r=128, L=143),
+    "Qwen3-32B": dict(d=5120, d_ff=25600, r=256, L=149),
+}
+
+
+# --------------------------------------------------------------------------- #
+# Parameters
+# --------------------------------------------------------------------------- #
+@dataclass
+class NetParams:
+    """Stacked DLR-Net parameters: V (L,r,d), U (L,d,r), w (L,d), alpha (L,)."""
+
+    V: torch.Tensor
+    U: torch.Tensor
+    w: torch.Tensor
+    alpha: torch.Tensor
+    eps: float = EPS
+
+    @property
+    def L(self) -> int:
+        return self.V.shape[0]
+
+    @property
+    def r(self) -> int:
+        return self.V.shape[1]
+
+    @property
+    def d(self) -> int:
+        return self.V.shape[2]
+
+    def to(self, dtype: torch.dtype) -> "NetParams":
+        return NetParams(self.V.to(dtype), self.U.to(dtype), self.w.to(dtype),
+                         self.alpha.to(dtype), self.eps)
+
+
+def seeded_params(d: int, r: int, L: int, seed: int, alpha: float = 0.01,
+                  gain_jitter: float = 0.0) -> NetParams:
+    """Draw parameters with the generator call order of dlr_lock/model.py:65-81.
+
+    The reference constructor draws all V_i (r,d) first, then all U_i (d,r),
+    with scales 1/sqrt(d) and 1/sqrt(r*L); gains are ones and every alpha is
+    ``alpha``.  With ``gain_jitter`` > 0 the gains become 1 + jitter*N(0,1),
+    drawn layer by layer after U (a stress setting, not a reference default).
+    """
+    torch.manual_seed(seed)
+    v_scale = 1.0 / math.sqrt(d)
+    u_scale = 1.0 / math.sqrt(r * L)
+    V = torch.stack([torch.randn(r, d) * v_scale for _ in range(L)])
+    U = torch.stack([torch.randn(d, r) * u_scale for _ in range(L)])
+    w = torch.ones(L, d)
+    if gain_jitter:
+        w = w + gain_jitter * torch.stack([torch.randn(d) for _ in range(L)])
+    a = torch.full((L,), float(alpha))
+    return NetParams(V, U, w, a)
+
+
+def seeded_case(d: int, r: int, L: int, M: int, seed: int, alpha: float = 0.01,
+                gain_jitter: float = 0.0):
+    """Parameters and an (M,d) input, both rounded to bf16 (returned as bf16)."""
+    p = seeded_params(d, r, L, seed, alpha, gain_jitter)
+    x = torch.randn(M, d)
+    return p.to(torch.bfloat16), x.to(torch.bfloat16)
+
+
+# --------------------------------------------------------------------------- #
+# Forward
+# --------------------------------------------------------------------------- #
+def _layer_loop(h: torch.Tensor, p: NetParams) -> torch.Tensor:
+    # One iteration = dlr_lock/model.py:96-100, in that op order.
+    for i in range(p.L):
+        mean_sq = (h * h).mean(dim=-1, keepdim=True)          # :96
+        normed = h * p.w[i] * torch.rsqrt(mean_sq + p.eps)    # :97
+        z = normed @ p.V[i].transpose(0, 1)                   # :98
+        dh = torch.nn.functional.silu(z) @ p.U[i].transpose(0, 1)  # :99
+        h = h + p.alpha[i] * dh                               # :100
+    return h
+
+
+@torch.no_grad()
+def forward_eager(x: torch.Tensor, p: NetParams) -> torch.Tensor:
+    """The reference's own forward in the parameter dtype (bf16 -> bf16 ops)."""
+    assert x.dtype == p.V.dtype
+    return _layer_loop(x, p)
+
+
+@torch.no_grad()
+def forward_fp32(x: torch.Tensor, p: NetParams) -> torch.Tensor:
+    """Same loop, every tensor widened to fp32 first; returns fp32."""
+    return _layer_loop(x.float(), p.to(torch.float32))
+
+
+# --------------------------------------------------------------------------- #
+# Weight folding (kernel-side format)
+# --------------------------------------------------------------------------- #
+@torch.no_grad()
+def fold_weights(p: NetParams):
+    """Fold the gain into V and alpha into U, once, as kernels/reference.py:77-79.
+
+    The reference rounds V, U and the gain to bf16, multiplies in fp32 (alpha
+    kept in fp32 after a cast from the parameter dtype) and rounds the product
+    to bf16.  Returned in the module's own layouts: V' (L,r,d), U' (L,d,r).
+    """
+    Vb = p.V.to(torch.bfloat16).float()
+    Ub = p.U.to(torch.bfloat16).float()
+    wb = p.w.to(torch.bfloat16).float()
+    af = p.alpha.detach().float()
+    Vf = (Vb * wb[:, None, :]).to(torch.bfloat16)
+    Uf = (Ub * af[:, None, None]).to(torch.bfloat16)
+    return Vf.contiguous(), Uf.contiguous()
+
+
+@torch.no_grad()
+def forward_folded_fp32(x: torch.Tensor, Vf: torch.Tensor, Uf: torch.Tensor,
+                        eps: float = EPS, round_h: bool = False) -> torch.Tensor:
+    """Kernel-side algebra of kernels/README.md:5-7 on folded weights, in fp32.
+
+    z = (h @ V'^T) * rstd ; h += silu(z) @ U'^T.  ``round_h`` re-rounds h to
+    bf16 after every layer, which is what a kernel that stores the activation
+    as bf16 on chip does.
+    """
+    h = x.float()
+    Vf = Vf.float()
+    Uf = Uf.float()
+    for i in range(Vf.shape[0]):
+        hb = h.to(torch.bfloat16).float()
+        rstd = torch.rsqrt((h * h).mean(dim=-1, keepdim=True) + eps)
+        z = (hb @ Vf[i].transpose(0, 1)) * rstd
+        s = torch.nn.functional.silu(z).to(torch.bfloat16).float()
+        h = h + s @ Uf[i].transpose(0, 1)
+        if round_h:
+            h = h.to(torch.bfloat16).float()
+    return h
+
+
+# --------------------------------------------------------------------------- #
+# Error metrics
+# --------------------------------------------------------------------------- #
+def rel_l2(y: torch.Tensor, ref: torch.Tensor) -> float:
+    """||y - ref|| / ||ref||  (kernels/bench/bench_paper.py:122-123)."""
+    y = y.double()
+    ref = ref.double()
+    return float((y - ref).norm() / ref.norm())
+
+
+def rel_l2_update(y: torch.Tensor, ref: torch.Tensor, x: torch.Tensor) -> float:
+    """Error of the *update*: ||(y-x) - (ref-x)|| / ||ref - x||.
+
+    With the benchmark's alpha=0.01 the whole stack moves the input by well
+    under one percent, so a kernel that returned its input would pass a 1e-2
+    total-error gate; it scores 1.0 here.
+    """
+    y = y.double()
+    ref = ref.double()
+    x = x.double()
+    den = (ref - x).norm()
+    return float((y - ref).norm() / den) if den > 0 else float((y - ref).norm())

@@ -1,0 +1,192 @@
+"""CUDA path (through the C ABI) against the oracle and the reference fixtures."""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import dlrnet_oracle as O
+
+from conftest import load_golden
+
+pytestmark = pytest.mark.gpu
+
+# Tolerances (relative L2, after the full L-layer stack).
+TOL_TOTAL = 1e-2        # vs the reference's own bf16 forward and vs its fp32 forward
+TOL_UPDATE_FP32H = 5e-2  # update-relative, for the path that carries h in fp32 on chip
+
+
+@pytest.fixture(scope="module")
+def D():
+    import dlr_lock_b200 as D
+    assert torch.cuda.is_available()
+    D.ops._lib.load()          # fails loudly if the extension was not built
+    return D
+
+
+def _run(D, p, x):
+    dev = torch.device("cuda:0")
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    y = D.ops.forward_folded(x.to(dev), Vf, Uf, p.eps)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    return y.cpu(), Vf.cpu(), Uf.cpu()
+
+
+@pytest.mark.parametrize("name", ["toy_d64_r8" if False else "toy_d256_r32", "toy_d256_r32_stress",
+                                  "toy_d512_r64_stress", "cfg1_d1024_r32", "cfg1_d1024_r32_stress",
+                                  "cfg2_d2048_r64", "cfg3_d4096_r128", "cfg4_d5120_r256"])
+def test_small_batch_against_reference_fixtures(D, name):
+    g = load_golden(name)
+    m = g["meta"]
+    p, x = O.seeded_case(m["d"], m["r"], m["L"], m["M"], m["seed"], m["alpha"], m["gain_jitter"])
+    assert torch.equal(x, g["x"])
+    y, Vf, Uf = _run(D, p, x)
+    # folding on the device is bit-identical to the reference packer's arithmetic
+    Vo, Uo = O.fold_weights(p)
+    assert torch.equal(Vf, Vo) and torch.equal(Uf, Uo)
+    assert O.rel_l2(y, g["y_bf16"]) <= (TOL_TOTAL if m["alpha"] < 0.5 else 2.5e-2)
+    assert O.rel_l2(y, g["y_fp32"]) <= TOL_TOTAL
+    assert O.rel_l2_update(y, g["y_fp32"], x) <= TOL_UPDATE_FP32H
+
+
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16, 31, 64])
+def test_row_counts_small(D, M):
+    p, x = O.seeded_case(512, 64, 9, M, seed=21, alpha=1.0, gain_jitter=0.1)
+    y, _, _ = _run(D, p, x)
+    want = O.forward_fp32(x, p)
+    assert O.rel_l2(y, want) <= 5e-3
+    assert O.rel_l2_update(y, want, x) <= 2e-2
+
+
+@pytest.mark.parametrize("d,r", [(256, 16), (1024, 32), (2048, 64), (1024, 128), (512, 256), (5120, 256)])
+def test_shapes(D, d, r):
+    p, x = O.seeded_case(d, r, 4, 7, seed=d + r, alpha=1.0, gain_jitter=0.1)
+    y, _, _ = _run(D, p, x)
+    want = O.forward_fp32(x, p)
+    assert O.rel_l2(y, want) <= 5e-3
+    assert O.rel_l2_update(y, want, x) <= 2e-2
+
+
+def test_identity_when_all_alphas_are_zero(D):
+    # examples/smoke_test.py:73-75: exact identity at alpha = 0
+    p, x = O.seeded_case(1024, 32, 7, 5, seed=4, alpha=0.0)
+    y, _, _ = _run(D, p, x)
+    assert torch.equal(y, x)
+
+
+def test_rows_are_independent_and_input_is_untouched(D):
+    p, x = O.seeded_case(1024, 32, 11, 24, seed=8, alpha=1.0)
+    dev = torch.device("cuda:0")
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    xd = x.to(dev)
+    keep = xd.clone()
+    y_all = D.ops.forward_folded(xd, Vf, Uf)
+    y_one = D.ops.forward_folded(xd[5:6], Vf, Uf)
+    perm = torch.randperm(24, device=dev)
+    y_perm = D.ops.forward_folded(xd[perm], Vf, Uf)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert torch.equal(xd, keep)
+    assert O.rel_l2(y_one.cpu(), y_all[5:6].cpu()) <= 1e-3
+    assert O.rel_l2(y_perm.cpu(), y_all[perm].cpu()) <= 1e-3
+
+
+def test_leading_dims_and_noncontiguous_input(D):
+    p, x = O.seeded_case(256, 32, 6, 12, seed=9, alpha=1.0)
+    dev = torch.device("cuda:0")
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    x3 = x.view(3, 4, 256).to(dev)
+    y3 = D.ops.forward_folded(x3, Vf, Uf)
+    assert y3.shape == x3.shape and y3.dtype == x3.dtype
+    xt = x3.transpose(0, 1)                      # non-contiguous view
+    yt = D.ops.forward_folded(xt, Vf, Uf)
+    torch.cuda.synchronize()
+    assert O.rel_l2(yt.cpu(), y3.transpose(0, 1).cpu()) <= 1e-3
+    want = O.forward_fp32(x, p).view(3, 4, 256)
+    assert O.rel_l2(y3.cpu(), want) <= 5e-3
+
+
+def test_reference_calling_conventions(D):
+    # fn(x, Vs, Us) with both stacks (L,R,D) (kernels/bench/bench_paper.py:97-101) and the
+    # packed-dict convention (kernels/kernels/triton_fused.py:68-92)
+    p, x = O.seeded_case(512, 64, 5, 6, seed=10, alpha=1.0)
+    dev = torch.device("cuda:0")
+    Vf, Uf = O.fold_weights(p)
+    want = D.ops.forward_folded(x.to(dev), Vf.to(dev), Uf.to(dev))
+    y1 = D.ops.forward_xvu(x.to(dev), Vf.to(dev), Uf.transpose(1, 2).contiguous().to(dev))
+    packed = {"Vs": Vf.transpose(1, 2).contiguous().to(dev), "Us": Uf.transpose(1, 2).contiguous().to(dev),
+              "L": 5, "D": 512, "R": 64, "premultiplied": True}
+    y2 = D.ops.dlrnet_fused(x.to(dev), packed)
+    torch.cuda.synchronize()
+    assert O.rel_l2(y1.cpu(), want.cpu()) <= 1e-3 and O.rel_l2(y2.cpu(), want.cpu()) <= 1e-3
+    with pytest.raises(ValueError):
+        D.ops.dlrnet_fused(x.to(dev), dict(packed, premultiplied=False))
+
+
+def test_module_fast_path_and_locked_model(D, tmp_path):
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    net = D.DLRNet(256, 32, 9, alpha_init=0.5).to(dev).to(torch.bfloat16).eval()
+    x = torch.randn(2, 5, 256, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        y_fast = net(x)
+        net.fast = False
+        y_slow = net(x)
+        net.fast = True
+    assert O.rel_l2(y_fast.cpu(), y_slow.cpu()) <= 1e-2
+    # parameters change -> folded cache is rebuilt
+    with torch.no_grad():
+        for a in net.alphas:
+            a.zero_()
+        assert torch.equal(net(x), x)
+    # gradients requested -> torch loop, gradient flows
+    xg = x.clone().requires_grad_(True)
+    net.train()
+    net(xg).float().sum().backward()
+    assert xg.grad is not None
+
+    from test_host_logic import _tiny_qwen3
+    path = _tiny_qwen3(str(tmp_path))
+    model = D.build_locked_model(path, rank=16, device="cuda:0", alpha_init=0.3, verbose=False).eval()
+    ids = torch.randint(0, 128, (2, 9), device=dev)
+    with torch.no_grad():
+        fast = model(ids).logits.float()
+        for layer in model.model.layers:
+            layer.mlp.dlrnet.fast = False
+        slow = model(ids).logits.float()
+    assert O.rel_l2(fast.cpu(), slow.cpu()) <= 2e-2
+
+
+def test_abi_argument_errors(D):
+    lib = D.ops._lib.load()
+    dev = torch.device("cuda:0")
+    x = torch.zeros(4, 256, dtype=torch.bfloat16, device=dev)
+    y = torch.empty_like(x)
+    V = torch.zeros(2, 32, 256, dtype=torch.bfloat16, device=dev)
+    U = torch.zeros(2, 256, 32, dtype=torch.bfloat16, device=dev)
+    ws = torch.zeros(1 << 20, dtype=torch.uint8, device=dev)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    vp = lambda t, off=0: ctypes.c_void_p(t.data_ptr() + off)
+    args = lambda **kw: [kw.get("x", vp(x)), vp(y), vp(V), vp(U), 4, 256, 32, 2, 1e-6, kw.get("ws", vp(ws)),
+                         kw.get("n", ws.numel()), vp(st), None]
+    assert lib.dlrb200_forward(*args()) == 0
+    assert lib.dlrb200_forward(*args(x=vp(x, 2))) == 3          # misaligned
+    assert lib.dlrb200_forward(*args(n=16)) == 4                # workspace too small
+    assert lib.dlrb200_forward(*args(x=vp(y))) == 1             # aliasing
+    torch.cuda.synchronize()
+    plan = D.ops.query(4, 4096, 128, 143)
+    assert plan.path == 1 and plan.grid * plan.stripe_cols == 4096
+
+
+def test_host_buffer_entry_point(D):
+    p, x = O.seeded_case(1024, 32, 6, 40, seed=12, alpha=1.0)
+    dev = torch.device("cuda:0")
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    xh = x.pin_memory()
+    yh = torch.empty_like(xh).pin_memory()
+    xd = torch.empty_like(x, device=dev)
+    yd = torch.empty_like(x, device=dev)
+    D.ops.forward_host(xh, yh, xd, yd, Vf, Uf)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert O.rel_l2(yh, O.forward_fp32(x, p)) <= 5e-3

@@ -1,0 +1,123 @@
+"""Host-side mirror of the reference API, on CPU."""
+import os
+
+import pytest
+import torch
+
+import dlr_lock_b200 as D
+from dlr_lock_b200 import registry, sharding
+from oracle import dlrnet_oracle as O
+
+from conftest import load_golden
+
+
+def test_module_matches_oracle_and_reference_fixture():
+    g = load_golden("toy_d256_r32_stress")
+    m = g["meta"]
+    p = O.seeded_params(m["d"], m["r"], m["L"], m["seed"], m["alpha"], m["gain_jitter"]).to(torch.bfloat16)
+    net = D.DLRNet(m["d"], m["r"], m["L"], alpha_init=m["alpha"])
+    sd = {}
+    for i in range(m["L"]):
+        sd[f"Vs.{i}"], sd[f"Us.{i}"], sd[f"rms_w.{i}"], sd[f"alphas.{i}"] = p.V[i], p.U[i], p.w[i], p.alpha[i]
+    net.load_state_dict(sd)                      # reference state_dict keys (dlr_lock/model.py:232-248)
+    net = net.to(torch.bfloat16)
+    with torch.no_grad():
+        y = net(g["x"])
+    assert O.rel_l2(y, g["y_bf16"]) <= 2e-3
+
+
+def test_invariants_of_the_reference_smoke_test():
+    # examples/smoke_test.py:65-98
+    d, r, depth = 64, 8, 12
+    net = D.DLRNet(d, r, depth, alpha_init=0.0)
+    assert sum(p.numel() for p in net.parameters()) == D.dlrnet_param_count(d, r, depth)
+    x = torch.randn(4, 7, d)
+    assert torch.equal(net(x), x)
+    net = D.DLRNet(d, r, depth, alpha_init=0.1)
+    xg = torch.randn(3, 5, d, requires_grad=True)
+    net.use_checkpoint = True
+    ya = net(xg)
+    ga = torch.autograd.grad(ya.sum(), xg)[0]
+    net.use_checkpoint = False
+    yb = net(xg)
+    gb = torch.autograd.grad(yb.sum(), xg)[0]
+    assert torch.allclose(ya, yb, atol=1e-6) and torch.allclose(ga, gb, atol=1e-6)
+    for dd, d_ff, rr, want in ((1024, 3072, 32, 141), (2048, 6144, 64, 142), (4096, 12288, 128, 143),
+                               (5120, 25600, 256, 149)):
+        assert D.compute_depth(dd, d_ff, rr) == want
+    cfg = D.dlrnet_config(1024, 3072, 32)
+    assert cfg["depth"] == 141 and cfg["params"] == D.dlrnet_param_count(1024, 32, 141)
+
+
+def test_cuda_only_entry_points_refuse_cpu_tensors():
+    x = torch.zeros(2, 64, dtype=torch.bfloat16)
+    V = torch.zeros(3, 16, 64, dtype=torch.bfloat16)
+    U = torch.zeros(3, 64, 16, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        D.ops.forward_folded(x, V, U)
+    with pytest.raises(ValueError):
+        D.ops.fold_weights(V, U, torch.ones(3, 64), torch.ones(3))
+
+
+def test_registry_covers_every_cell():
+    for model in ("Qwen3-0.6B", "Qwen3-1.7B", "Qwen3-8B", "Qwen3-32B"):
+        for B in (1, 2, 8, 64, 65, 1024, 6000, 8192, 131072):
+            e = registry.resolve(model, B)
+            assert e is not None and set(e) >= {"B_lo", "B_hi", "kernel", "callable", "config", "note"}
+            mod, fn = e["callable"].rsplit(".", 1)
+            assert callable(getattr(__import__(mod, fromlist=[fn]), fn))
+    assert registry.resolve("Qwen3-8B", 0) is None
+    assert registry.resolve("nope", 4) is None
+
+
+@pytest.mark.parametrize("M,world,tile", [(8192, 8, 128), (1000, 4, 128), (3, 8, 1), (0, 2, 16), (129, 2, 128)])
+def test_row_blocks_partition(M, world, tile):
+    blocks = sharding.row_blocks(M, world, tile)
+    assert len(blocks) == world and blocks[0][0] == 0 and blocks[-1][1] == M
+    for (a, b), (c, _) in zip(blocks, blocks[1:]):
+        assert a <= b == c
+    for a, b in blocks[:-1]:
+        assert (b - a) % tile == 0 or b == M
+
+
+def _tiny_qwen3(tmp_path):
+    from transformers import AutoConfig, AutoModelForCausalLM
+    cfg = AutoConfig.for_model("qwen3", vocab_size=128, hidden_size=64, intermediate_size=256,
+                               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                               head_dim=16, max_position_embeddings=64, tie_word_embeddings=True)
+    path = os.path.join(tmp_path, "tiny")
+    AutoModelForCausalLM.from_config(cfg).save_pretrained(path)
+    return path
+
+
+def test_surgery_and_checkpoint_round_trip(tmp_path):
+    # examples/smoke_test.py:101-124 and 156-188, on a random two-layer decoder
+    path = _tiny_qwen3(str(tmp_path))
+    torch.manual_seed(0)
+    model = D.build_locked_model(path, rank=8, torch_dtype=torch.float32, alpha_init=0.1, verbose=False).eval()
+    depth = D.compute_depth(64, 256, 8)
+    assert model.model.layers[0].mlp.dlrnet.depth == depth
+    seen = {}
+    layer = model.model.layers[1]
+    h1 = layer.mlp.register_forward_hook(lambda m, a, o: seen.__setitem__("h", a[0].detach()))
+    h2 = layer.register_forward_hook(lambda m, a, o: seen.__setitem__("out", (o[0] if isinstance(o, tuple) else o).detach()))
+    ids = torch.randint(0, 128, (2, 9))
+    with torch.no_grad():
+        logits = model(ids).logits
+    h1.remove(); h2.remove()
+    with torch.no_grad():
+        want = layer.mlp.dlrnet(seen["h"])
+    assert torch.allclose(seen["out"], want, atol=1e-5)
+
+    ckpt = os.path.join(str(tmp_path), "ckpt")
+    assert D.save_dlrnet_weights(model, ckpt) == 2
+    assert sorted(os.listdir(ckpt)) == ["layer00.pt", "layer01.pt"]
+    sd = torch.load(os.path.join(ckpt, "layer00.pt"), weights_only=True)
+    assert {"Vs.0", "Us.0", "rms_w.0", "alphas.0"} <= set(sd)
+    fresh = D.build_locked_model(path, rank=8, torch_dtype=torch.float32, alpha_init=0.0, verbose=False).eval()
+    assert D.load_dlrnet_weights(fresh, ckpt) == 2
+    with torch.no_grad():
+        again = fresh(ids).logits
+    assert torch.allclose(logits, again, atol=1e-6)
+    assert D.set_checkpointing(fresh, False) == 2
+    assert D.accelerate_locked_model(fresh) == 2
