@@ -202,13 +202,14 @@ def _cluster_case(D, d, r, L, M, seed, alpha, jitter=0.0):
     return p, x, y, Vf, Uf
 
 
-@pytest.mark.parametrize("d,r,M", [(512, 32, 128), (512, 64, 65), (512, 128, 200), (1024, 32, 130),
-                                   (2048, 64, 384), (4096, 128, 129), (4096, 64, 256), (4096, 32, 128)])
+@pytest.mark.parametrize("d,r,M", [(1024, 32, 130), (1024, 64, 65), (2048, 64, 384), (2048, 128, 200),
+                                   (4096, 128, 129), (4096, 128, 700), (1024, 32, 1100)])
 def test_cluster_path_shapes(D, d, r, M):
     p, x, y, Vf, Uf = _cluster_case(D, d, r, 5, M, seed=d + r + M, alpha=1.0, jitter=0.1)
-    # same algebra with the activation re-rounded to bf16 after every layer
+    # same algebra with the activation re-rounded to bf16 after every layer (the bf16
+    # transport of the partial z adds a little on top of this model)
     model = O.forward_folded_fp32(x, Vf, Uf, p.eps, round_h=True)
-    assert O.rel_l2(y, model) <= 3e-3
+    assert O.rel_l2(y, model) <= 6e-3
     want = O.forward_fp32(x, p)
     assert O.rel_l2(y, want) <= 1e-2
     assert O.rel_l2_update(y, want, x) <= 5e-2
