@@ -16,10 +16,13 @@
 //       h += dh ; sumsq_part = sum h^2                        fused epilogue out of TMEM
 //
 // Two tiles per CTA.  The exchange X is a latency chain during which a tile
-// has no tensor work, so every CTA carries two independent row tiles, tile B
-// half a layer behind tile A: the MMA warp issues V(A,l) U(B,l-1) V(B,l) U(A,l),
-// and each tile's exchange and epilogue run under the other tile's
-// contractions.
+// has no tensor work, so every CTA runs TWO independent pipelines, one per row
+// tile, each with its own weight ring, TMA warp, MMA warp and four epilogue
+// warps; whenever one tile waits on its exchange or epilogue the other tile's
+// contractions use the tensor core.  Two issuing warps are also what it takes
+// to keep the tensor core busy here: one thread issues a 128x128x16
+// tcgen05.mma only every ~130 cycles (measured), half of what the pipe can
+// execute.
 //
 // On-chip residency.  Per tile, 128 tensor-memory columns hold the activation
 // stripe as packed bf16 (the A operand of the V contraction, straight from
@@ -37,10 +40,12 @@
 // directly in the core-matrix layout the MMA reads (8 rows x 16 bytes
 // contiguous, no swizzle), which also makes each warp's stores contiguous.
 //
-// Roles.  Warp 0 streams weight tiles with TMA into a ring of 16 KB stages;
-// one lane of warp 1 issues all MMAs; warps 2-5 serve tile A and warps 6-9
-// tile B, one thread per row.  All waits are bounded mbarrier waits; a wait
-// that gives up records a status word and every role drains to a common exit.
+// Roles.  Per tile: one warp streams 8 KB weight tiles (32 K-columns, 64-byte
+// swizzle) with TMA into that tile's ring, one lane of another warp issues the
+// tile's MMAs, four warps (one thread per row) run exchange and epilogue.
+// Warps 0/1 = TMA/MMA of tile A, 2/3 = TMA/MMA of tile B, 4-7 and 8-11 the two
+// epilogue groups.  All waits are bounded mbarrier waits; a wait that gives up
+// records a status word and every role drains to a common exit.
 #include <cstdlib>
 #include <cstring>
 
@@ -52,12 +57,13 @@ namespace dlr {
 namespace {
 
 constexpr int kRows = 128;
-constexpr int kKT = 4;               // 64-column K tiles per stripe
-constexpr int kStripe = 64 * kKT;    // 256 columns per CTA
+constexpr int kStripe = 256;         // columns of the model width per CTA
+constexpr int kWK = 32;              // K columns per weight tile (one 64-byte swizzle span)
+constexpr int kVT = kStripe / kWK;   // V tiles per layer
 constexpr int kNCH = kStripe / 128;  // 128-column output chunks per stripe
-constexpr int kStageBytes = 16384;
-constexpr int kMaxStages = 8;
-constexpr int kThreads = 320;
+constexpr int kStageBytes = 8192;
+constexpr int kMaxStages = 8;        // per tile
+constexpr int kThreads = 384;
 constexpr uint32_t kTileCols = 256;  // tensor-memory columns per tile
 constexpr uint32_t kHOff = 0;        // packed bf16 activation: 128 columns
 constexpr uint32_t kAccOff = 128;    // fp32 accumulator: 128 columns
@@ -77,21 +83,16 @@ struct ClusterParams {
 
 template <int R>
 struct CCfg {
-    static constexpr int KW = R < 64 ? R : 64;     // K columns per s / U tile
-    static constexpr int UK = R / KW;              // K tiles of the U contraction
-    static constexpr int ROWB = KW * 2;            // bytes per tile row
-    static constexpr int S_TILE_BYTES = kRows * ROWB;
     static constexpr int S_BYTES = kRows * R * 2;  // s tile (A operand of the U contraction)
     static constexpr int NCK = R / 8;              // 16-byte K chunks per row
     static constexpr int S_GROUP_BYTES = NCK * 128;          // one 8-row group of the s tile
     static constexpr int R_GROUP_BYTES = (NCK + 1) * 128;    // same plus one chunk for the sums of squares
     static constexpr int RECV_BYTES = (kRows / 8) * R_GROUP_BYTES;
-    static constexpr int V_CHUNK_BYTES = R * 128;
-    static constexpr int U_CHUNK_BYTES = 128 * ROWB;
-    static constexpr int SWZ_BITS = KW == 64 ? 3 : 2;
-    static constexpr uint32_t U_LAYOUT = KW == 64 ? 2u : 4u;   // descriptor layout type
-    static constexpr uint32_t U_SBO = 8 * ROWB;                // bytes between 8-row groups
-    static constexpr int LOADS_PER_LAYER = kKT + kNCH * UK;
+    static constexpr int V_TILE_BYTES = R * kWK * 2;         // R rows x 32 K-columns
+    static constexpr int U_TILE_BYTES = 128 * kWK * 2;       // 128 rows x 32 K-columns
+    static constexpr int UT = R / kWK;                       // U tiles per 128-column chunk
+    static constexpr uint32_t W_LAYOUT = 4u;                 // descriptor layout type: 64-byte swizzle
+    static constexpr uint32_t W_SBO = 8 * kWK * 2;           // bytes between 8-row groups of a weight tile
 };
 
 // per-tile shared-memory bytes besides the ring: the s tile and the receive buffer
@@ -158,6 +159,10 @@ __device__ __forceinline__ uint64_t umma_desc_nosw(uint32_t saddr, uint32_t lbo,
     return d;
 }
 
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
+
 #define DLR_CLK() (p.prof ? clock64() : 0ll)
 
 struct Waiter {
@@ -189,24 +194,23 @@ struct TileBars {
     uint64_t h_ready;      // epilogue -> MMA: activation stripe updated in tensor memory
 };
 
-template <int R>
+template <int R, int CS>
 __global__ void __launch_bounds__(kThreads, 1)
 dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmU,
                    ClusterParams p) {
     using C = CCfg<R>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int S = p.stages;
-    const int CS = p.cs;
-    const int rows_own = kRows / CS;
-    uint8_t* ring = smem;
-    uint8_t* tile_mem = ring + size_t(S) * kStageBytes;
+    const int S = p.stages;                       // ring stages per tile
+    constexpr int rows_own = kRows / CS;
+    uint8_t* ring = smem;                         // [2][S][kStageBytes]
+    uint8_t* tile_mem = ring + size_t(2 * S) * kStageBytes;
     // per tile: [s tile : S_BYTES][recv : RECV_BYTES]
     constexpr int tile_stride = tile_bytes(R);
     uint64_t* bars = reinterpret_cast<uint64_t*>(tile_mem + 2 * size_t(tile_stride));
-    uint64_t* ring_full = bars;                 // [kMaxStages]
-    uint64_t* ring_empty = bars + kMaxStages;   // [kMaxStages]
-    TileBars* tb = reinterpret_cast<TileBars*>(bars + 2 * kMaxStages);   // [2]
+    uint64_t* ring_full = bars;                   // [2][kMaxStages]
+    uint64_t* ring_empty = bars + 2 * kMaxStages; // [2][kMaxStages]
+    TileBars* tb = reinterpret_cast<TileBars*>(bars + 4 * kMaxStages);   // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tb + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -219,7 +223,7 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
     const Waiter w{abort_flag, p.spin_limit >> 2};
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kMaxStages; ++s) {
+        for (int s = 0; s < 2 * kMaxStages; ++s) {
             mbar_init(smem_u32(&ring_full[s]), 1);
             mbar_init(smem_u32(&ring_empty[s]), 1);
         }
@@ -246,147 +250,139 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
     cluster_wait_acquire();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t ring_s = smem_u32(ring);
     const uint32_t tile_s = smem_u32(tile_mem);
 
     int err = 0;
     int err_layer = 0;
 
-    if (warp == 0) {
-        // =============================== TMA producer ===============================
-        if (lane == 0) {
-            uint32_t n = 0;
-            long long pw = 0;
-            // phase order per layer l: V(A,l), U(B,l-1), V(B,l), U(A,l); a trailing U(B,L-1)
-            auto load_phase = [&](bool is_v, int l) {
-                const int cnt = is_v ? kKT : kNCH * C::UK;
-                for (int i = 0; i < cnt && !err; ++i, ++n) {
-                    const uint32_t st = n % uint32_t(S);
-                    const uint32_t ph = (n / uint32_t(S)) & 1u;
-                    const long long t0 = DLR_CLK();
-                    if (!w.cta(smem_u32(&ring_empty[st]), ph ^ 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; err_layer = l; break; }
-                    pw += DLR_CLK() - t0;
-                    const uint32_t bar = smem_u32(&ring_full[st]);
-                    const uint32_t dst = ring_s + st * kStageBytes;
-                    if (is_v) {
-                        mbar_arrive_expect_tx(bar, C::V_CHUNK_BYTES);
-                        tma_load_2d(dst, &tmV, stripe0 + 64 * i, l * R, bar);
-                    } else {
-                        const int nc = i / C::UK, kh = i % C::UK;
-                        mbar_arrive_expect_tx(bar, C::U_CHUNK_BYTES);
-                        tma_load_2d(dst, &tmU, kh * C::KW, l * p.d + stripe0 + 128 * nc, bar);
+    if (warp < 4) {
+        const int t = warp >> 1;                  // tile served by this warp
+        const uint32_t ring_s = smem_u32(ring) + uint32_t(t * S) * kStageBytes;
+        uint64_t* rfull = ring_full + t * kMaxStages;
+        uint64_t* rempty = ring_empty + t * kMaxStages;
+        if ((warp & 1) == 0) {
+            // =============================== TMA producer of tile t =====================
+            if (lane == 0) {
+                uint32_t n = 0;
+                long long pw = 0;
+                for (int pair = cluster_id; pair < p.num_pairs && !err; pair += num_clusters) {
+                    for (int l = 0; l < p.L && !err; ++l) {
+                        for (int i = 0; i < kVT + kNCH * C::UT; ++i, ++n) {
+                            const uint32_t st = n % uint32_t(S);
+                            const uint32_t ph = (n / uint32_t(S)) & 1u;
+                            const long long t0 = DLR_CLK();
+                            if (!w.cta(smem_u32(&rempty[st]), ph ^ 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; err_layer = l; break; }
+                            pw += DLR_CLK() - t0;
+                            const uint32_t bar = smem_u32(&rfull[st]);
+                            const uint32_t dst = ring_s + st * kStageBytes;
+                            if (i < kVT) {
+                                mbar_arrive_expect_tx(bar, C::V_TILE_BYTES);
+                                tma_load_2d(dst, &tmV, stripe0 + kWK * i, l * R, bar);
+                                // pull the same tile of the NEXT layer into L2 (tile A's producer only:
+                                // both tiles read the same weights)
+                                if (t == 0 && l + 1 < p.L) tma_prefetch_2d(&tmV, stripe0 + kWK * i, (l + 1) * R);
+                            } else {
+                                const int j = i - kVT;
+                                const int nc = j / C::UT, kq = j % C::UT;
+                                mbar_arrive_expect_tx(bar, C::U_TILE_BYTES);
+                                tma_load_2d(dst, &tmU, kq * kWK, l * p.d + stripe0 + 128 * nc, bar);
+                                if (t == 0 && l + 1 < p.L) tma_prefetch_2d(&tmU, kq * kWK, (l + 1) * p.d + stripe0 + 128 * nc);
+                            }
+                        }
                     }
                 }
-            };
-            for (int pair = cluster_id; pair < p.num_pairs && !err; pair += num_clusters) {
-                for (int l = 0; l <= p.L && !err; ++l) {
-                    if (l < p.L) load_phase(true, l);
-                    if (l >= 1 && !err) load_phase(false, l - 1);
-                    if (l < p.L && !err) load_phase(true, l);
-                    if (l < p.L && !err) load_phase(false, l);
+                if (p.prof) p.prof[(blockIdx.x * 6 + t) * 16 + 0] = (unsigned long long)pw;
+                if (err) {
+                    // copies issued before giving up still land in this CTA's ring:
+                    // wait (bounded) for them before leaving.
+                    for (uint32_t back = 1; back <= uint32_t(S) && back <= n; ++back) {
+                        const uint32_t m = n - back;
+                        mbar_wait(smem_u32(&rfull[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, p.spin_limit >> 6);
+                    }
                 }
             }
-            if (p.prof) p.prof[(blockIdx.x * 4 + 0) * 16 + 0] = (unsigned long long)pw;
-            if (err) {
-                // copies issued before giving up still land in this CTA's ring:
-                // wait (bounded) for them before leaving.
-                for (uint32_t back = 1; back <= uint32_t(S) && back <= n; ++back) {
-                    const uint32_t m = n - back;
-                    mbar_wait(smem_u32(&ring_full[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, p.spin_limit >> 6);
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // =============================== MMA issuer =================================
-        if (lane == 0) {
-            const uint32_t idesc_v = umma_idesc_bf16(128, R);
-            const uint32_t idesc_u = umma_idesc_bf16(128, 128);
-            uint32_t n = 0;                      // ring position of the next weight tile
-            uint32_t c_h[2] = {0, 0}, c_s[2] = {0, 0}, c_e[2] = {0, 0};
-            long long m[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            const long long mstart = DLR_CLK();
-            // V contraction of tile t: accumulator = h . V'^T over the 4 K tiles of the stripe
-            auto v_phase = [&](int t, int l) {
-                err_layer = l;
-                const uint32_t tcol = tmem_base + uint32_t(t) * kTileCols;
-                long long t0 = DLR_CLK();
-                if (!w.cta(smem_u32(&tb[t].h_ready), c_h[t] & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; return; }
-                ++c_h[t];
-                tc_fence_after();
-                m[0] += DLR_CLK() - t0;
-                t0 = DLR_CLK();
-                for (int kt = 0; kt < kKT; ++kt, ++n) {
-                    const uint32_t st = n % uint32_t(S);
-                    const long long r0 = DLR_CLK();
-                    if (!w.cta(smem_u32(&ring_full[st]), (n / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; return; }
-                    m[4] += DLR_CLK() - r0;
-                    tc_fence_after();
-                    const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, 2u, 1024u);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_ts(tcol + kAccOff, tcol + kHOff + uint32_t(kt * 32 + k * 8), bdesc + uint64_t(2 * k), idesc_v,
-                                (kt | k) ? 1u : 0u);
-                    umma_commit(smem_u32(&ring_empty[st]));
-                }
-                umma_commit(smem_u32(&tb[t].z_full));
-                m[1] += DLR_CLK() - t0;
-            };
-            // U contraction of tile t: two 128-column chunks through the one accumulator
-            auto u_phase = [&](int t, int l) {
-                err_layer = l;
+        } else {
+            // =============================== MMA issuer of tile t =======================
+            if (lane == 0) {
+                const uint32_t idesc_v = umma_idesc_bf16(128, R);
+                const uint32_t idesc_u = umma_idesc_bf16(128, 128);
                 const uint32_t tcol = tmem_base + uint32_t(t) * kTileCols;
                 const uint32_t sb = tile_s + uint32_t(t) * uint32_t(tile_stride);
-                long long t0 = DLR_CLK();
-                if (!w.cluster(smem_u32(&tb[t].s_full), c_s[t] & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; return; }
-                ++c_s[t];
-                tc_fence_after();
-                m[2] += DLR_CLK() - t0;
-                t0 = DLR_CLK();
-                for (int nc = 0; nc < kNCH; ++nc) {
-                    const long long a0 = DLR_CLK();
-                    if (!w.cta(smem_u32(&tb[t].acc_empty), c_e[t] & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; return; }
-                    ++c_e[t];
-                    tc_fence_after();
-                    m[6] += DLR_CLK() - a0;
-                    for (int kh = 0; kh < C::UK; ++kh, ++n) {
-                        const uint32_t st = n % uint32_t(S);
-                        const long long r0 = DLR_CLK();
-                        if (!w.cta(smem_u32(&ring_full[st]), (n / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; return; }
-                        m[5] += DLR_CLK() - r0;
+                uint32_t n = 0;                      // ring position of the next weight tile
+                uint32_t c_h = 0, c_s = 0, c_e = 0;
+                long long m[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                const long long mstart = DLR_CLK();
+                for (int pair = cluster_id; pair < p.num_pairs && !err; pair += num_clusters) {
+                    for (int l = 0; l < p.L && !err; ++l) {
+                        err_layer = l;
+                        // ---- V contraction: accumulator = h . V'^T over the 8 K tiles of the stripe
+                        long long t0 = DLR_CLK();
+                        if (!w.cta(smem_u32(&tb[t].h_ready), c_h & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        ++c_h;
                         tc_fence_after();
-                        const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, C::U_LAYOUT, C::U_SBO);
+                        long long t1 = DLR_CLK();
+                        m[0] += t1 - t0;
+                        for (int kt = 0; kt < kVT && !err; ++kt, ++n) {
+                            const uint32_t st = n % uint32_t(S);
+                            const long long r0 = DLR_CLK();
+                            if (!w.cta(smem_u32(&rfull[st]), (n / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                            m[4] += DLR_CLK() - r0;
+                            tc_fence_after();
+                            const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, C::W_LAYOUT, C::W_SBO);
 #pragma unroll
-                        for (int k = 0; k < C::KW / 16; ++k) {
-                            // K step ks of the s tile: two 16-byte chunks, 128 bytes apart
-                            const int ks = kh * (C::KW / 16) + k;
-                            const uint64_t adesc = umma_desc_nosw(sb + uint32_t(ks) * 256u, 128u, C::S_GROUP_BYTES);
-                            umma_ss(tcol + kAccOff, adesc, bdesc + uint64_t(2 * k), idesc_u, (kh | k) ? 1u : 0u);
+                            for (int k = 0; k < kWK / 16; ++k)
+                                umma_ts(tcol + kAccOff, tcol + kHOff + uint32_t(kt * (kWK / 2) + k * 8), bdesc + uint64_t(2 * k),
+                                        idesc_v, (kt | k) ? 1u : 0u);
+                            umma_commit(smem_u32(&rempty[st]));
                         }
-                        umma_commit(smem_u32(&ring_empty[st]));
+                        if (err) break;
+                        umma_commit(smem_u32(&tb[t].z_full));
+                        t0 = DLR_CLK();
+                        m[1] += t0 - t1;
+                        // ---- U contraction: two 128-column chunks through the one accumulator
+                        if (!w.cluster(smem_u32(&tb[t].s_full), c_s & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        ++c_s;
+                        tc_fence_after();
+                        t1 = DLR_CLK();
+                        m[2] += t1 - t0;
+                        for (int nc = 0; nc < kNCH && !err; ++nc) {
+                            const long long a0 = DLR_CLK();
+                            if (!w.cta(smem_u32(&tb[t].acc_empty), c_e & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                            ++c_e;
+                            tc_fence_after();
+                            m[6] += DLR_CLK() - a0;
+                            for (int kq = 0; kq < C::UT && !err; ++kq, ++n) {
+                                const uint32_t st = n % uint32_t(S);
+                                const long long r0 = DLR_CLK();
+                                if (!w.cta(smem_u32(&rfull[st]), (n / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                                m[5] += DLR_CLK() - r0;
+                                tc_fence_after();
+                                const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, C::W_LAYOUT, C::W_SBO);
+#pragma unroll
+                                for (int k = 0; k < kWK / 16; ++k) {
+                                    // K step ks of the s tile: two 16-byte chunks, 128 bytes apart
+                                    const int ks = kq * (kWK / 16) + k;
+                                    const uint64_t adesc = umma_desc_nosw(sb + uint32_t(ks) * 256u, 128u, C::S_GROUP_BYTES);
+                                    umma_ss(tcol + kAccOff, adesc, bdesc + uint64_t(2 * k), idesc_u, (kq | k) ? 1u : 0u);
+                                }
+                                umma_commit(smem_u32(&rempty[st]));
+                            }
+                            if (err) break;
+                            umma_commit(smem_u32(&tb[t].dh_full));
+                        }
+                        m[3] += DLR_CLK() - t1;
                     }
-                    umma_commit(smem_u32(&tb[t].dh_full));
                 }
-                m[3] += DLR_CLK() - t0;
-            };
-            // Tile B runs half a layer behind tile A, so that each tile's exchange and
-            // epilogue fall under the other tile's contractions.
-            for (int pair = cluster_id; pair < p.num_pairs && !err; pair += num_clusters) {
-                for (int l = 0; l <= p.L && !err; ++l) {
-                    if (l < p.L) v_phase(0, l);
-                    if (l >= 1 && !err) u_phase(1, l - 1);
-                    if (l < p.L && !err) v_phase(1, l);
-                    if (l < p.L && !err) u_phase(0, l);
+                if (p.prof) {
+                    m[7] = DLR_CLK() - mstart;
+                    for (int k = 0; k < 8; ++k) p.prof[(blockIdx.x * 6 + 2 + t) * 16 + k] = (unsigned long long)m[k];
                 }
-            }
-            if (p.prof) {
-                m[7] = DLR_CLK() - mstart;
-                for (int k = 0; k < 8; ++k) p.prof[(blockIdx.x * 4 + 1) * 16 + k] = (unsigned long long)m[k];
             }
         }
     } else {
         // =============================== epilogue warps =============================
-        const int t = (warp - 2) >> 2;               // tile served by this warp group
-        const int gw = (warp - 2) & 3;               // warp inside the group
+        const int t = (warp - 4) >> 2;               // tile served by this warp group
+        const int gw = (warp - 4) & 3;               // warp inside the group
         const int gt = gw * 32 + lane;               // thread inside the group, 0..127
         const int q = warp & 3;                      // tensor-memory lane quadrant of this warp
         const int er = 32 * q + lane;                // row of the tile this thread owns
@@ -397,11 +393,11 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
         TileBars& B = tb[t];
         const int owner = er / rows_own;
         const int lr = er % rows_own;
-        const int groups_own = rows_own / 8;             // 8-row groups per owner
-        const uint32_t src_bytes = uint32_t(groups_own) * C::R_GROUP_BYTES;   // one source's block in recv
-        const int items = rows_own * C::NCK / 128;       // 16-byte chunks of s per thread in the reduce
+        constexpr int groups_own = rows_own / 8;         // 8-row groups per owner
+        constexpr uint32_t src_bytes = uint32_t(groups_own) * C::R_GROUP_BYTES;   // one source's block in recv
+        constexpr int items = rows_own * C::NCK / 128;   // 16-byte chunks of s per thread in the reduce
         uint32_t c_z = 0, c_recv = 0, c_dh = 0;
-        long long e[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+        long long e[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const long long estart = DLR_CLK();
 
         for (int pair = cluster_id; pair < p.num_pairs && !err; pair += num_clusters) {
@@ -437,7 +433,7 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
             for (int l = 0; l < p.L && !err; ++l) {
                 err_layer = l;
                 long long t0 = DLR_CLK();
-                // ---- partial z of this row: accumulator -> bf16 staging in the operand tile layout
+                // ---- partial z of this row: accumulator -> bf16 -> the row's owner
                 if (!__all_sync(0xffffffffu, w.cta(smem_u32(&B.z_full), c_z & 1u))) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                 ++c_z;
                 tc_fence_after();
@@ -475,6 +471,7 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                 t1 = DLR_CLK();
                 e[2] += t1 - t0;
                 if (gt == 0) mbar_arrive_expect_tx(smem_u32(&B.s_full), C::S_BYTES);      // arm this layer's s tile
+#pragma unroll
                 for (int it = 0; it < items; ++it) {
                     const int i = gt + 128 * it;
                     const int r8 = i & 7;
@@ -485,6 +482,7 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                     float a[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) a[j] = 0.f;
+#pragma unroll
                     for (int src = 0; src < CS; ++src) {
                         const uint8_t* bp = base + size_t(src) * src_bytes;
                         const uint4 u = *reinterpret_cast<const uint4*>(bp + c * 128);
@@ -502,6 +500,7 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                     // row (rank*rows_own + 8*gl + r8) of the s tile, chunk c, in every CTA of the cluster
                     const uint32_t soff = uint32_t(int(rank) * groups_own + gl) * C::S_GROUP_BYTES + uint32_t(c) * 128u +
                                           uint32_t(r8) * 16u;
+#pragma unroll
                     for (int dc = 0; dc < CS; ++dc)
                         st_async_v4(mapa(sbuf_s + soff, uint32_t(dc)), p0, p1, p2, p3,
                                     mapa(smem_u32(&B.s_full), uint32_t(dc)));
@@ -527,10 +526,8 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                         for (int j = 0; j < 16; ++j) {
                             const float lo = bf16lo_to_f(hp[j]) + __uint_as_float(dh[2 * j]);
                             const float hi = bf16hi_to_f(hp[j]) + __uint_as_float(dh[2 * j + 1]);
-                            const uint32_t pk = pack_bf16x2(lo, hi);
-                            const float rl = bf16lo_to_f(pk), rh = bf16hi_to_f(pk);
-                            ssq_new += rl * rl + rh * rh;
-                            hp[j] = pk;
+                            ssq_new += lo * lo + hi * hi;
+                            hp[j] = pack_bf16x2(lo, hi);
                         }
                         tmem_st16(tl + kHOff + uint32_t(64 * nc + 16 * c), hp);
                     }
@@ -564,7 +561,7 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
         }
         if (p.prof && gt == 0) {
             e[7] = DLR_CLK() - estart;
-            for (int k = 0; k < 16; ++k) p.prof[(blockIdx.x * 4 + 2 + t) * 16 + k] = (unsigned long long)e[k];
+            for (int k = 0; k < 8; ++k) p.prof[(blockIdx.x * 6 + 4 + t) * 16 + k] = (unsigned long long)e[k];
         }
     }
 
@@ -584,18 +581,19 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
     }
 }
 
-template <int R>
+template <int R, int CS>
 int launch_cluster(void* enc, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int L, float eps,
                    int* status_dev, cudaStream_t stream, int num_sms, int smem_optin, unsigned int spin_limit,
                    dlrb200_plan* plan_only, unsigned long long* prof) {
     using C = CCfg<R>;
-    auto kern = dlr_cluster_kernel<R>;
-    const int cs = d / kStripe;
+    auto kern = dlr_cluster_kernel<R, CS>;
+    const int cs = CS;
+    if (d != CS * kStripe) return DLRB200_ERR_UNSUPPORTED_SHAPE;
     const int fixed = 2 * tile_bytes(R) + 1024 /*barriers*/ + 1024 /*alignment*/;
-    int stages = (smem_optin - fixed) / kStageBytes;
+    int stages = (smem_optin - fixed) / (2 * kStageBytes);      // per tile
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 3) return DLRB200_ERR_UNSUPPORTED_SHAPE;
-    const int smem = stages * kStageBytes + fixed;
+    const int smem = 2 * stages * kStageBytes + fixed;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return DLRB200_ERR_CUDA;
     if (cs > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
@@ -644,8 +642,8 @@ int launch_cluster(void* enc, const void* x, void* y, const void* Vp, const void
     p.cs = cs;
     p.prof = prof;
     CUtensorMap tmV, tmU;
-    if (!encode_2d_bf16(enc, &tmV, Vp, uint64_t(d), uint64_t(L) * R, 64, R, 128) ||
-        !encode_2d_bf16(enc, &tmU, Up, uint64_t(R), uint64_t(L) * d, C::KW, 128, C::KW * 2))
+    if (!encode_2d_bf16(enc, &tmV, Vp, uint64_t(d), uint64_t(L) * R, kWK, R, kWK * 2) ||
+        !encode_2d_bf16(enc, &tmU, Up, uint64_t(R), uint64_t(L) * d, kWK, 128, kWK * 2))
         return DLRB200_ERR_CUDA;
     const cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, tmV, tmU, p);
     return ce == cudaSuccess ? DLRB200_OK : DLRB200_ERR_CUDA;
@@ -654,17 +652,23 @@ int launch_cluster(void* enc, const void* x, void* y, const void* Vp, const void
 int dispatch(void* enc, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r, int L, float eps,
              int* status_dev, cudaStream_t stream, int num_sms, int smem_optin, unsigned int spin_limit,
              dlrb200_plan* plan_only, unsigned long long* prof) {
-    switch (r) {
-        case 32: return launch_cluster<32>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
-        case 64: return launch_cluster<64>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
-        case 128: return launch_cluster<128>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
-    }
+#define DLR_CASE(RR, CC)                                                                                          \
+    if (r == RR && d == CC * kStripe)                                                                             \
+        return launch_cluster<RR, CC>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin,   \
+                                      spin_limit, plan_only, prof);
+    DLR_CASE(32, 4)
+    DLR_CASE(64, 4)
+    DLR_CASE(64, 8)
+    DLR_CASE(128, 4)
+    DLR_CASE(128, 8)
+    DLR_CASE(128, 16)
+#undef DLR_CASE
     return DLRB200_ERR_UNSUPPORTED_SHAPE;
 }
 
 // Debug aid: with DLRB200_PROFILE=1 in the environment every CTA writes cycle
-// counts of its phases (4 roles x 16 counters) at offset 256 of the workspace.
-constexpr size_t kProfBytes = 256 + size_t(256) * 4 * 16 * 8;
+// counts of its phases (6 roles x 16 counters) at offset 256 of the workspace.
+constexpr size_t kProfBytes = 256 + size_t(256) * 6 * 16 * 8;
 
 bool profiling() {
     const char* v = std::getenv("DLRB200_PROFILE");
