@@ -1,51 +1,49 @@
 // Large-batch ("prefill") DLR-Net forward on thread-block clusters with tcgen05
 // tensor cores and tensor memory.
 //
-// Work split.  A cluster of CS = d/256 CTAs (4, 8 or 16) walks all L layers for
-// a PAIR of 128-row tiles; CTA `rank` owns columns [256*rank, 256*rank+256) of
-// the model width for BOTH contractions of a layer (K-stripe of the V
-// contraction, N-stripe of the U contraction - the reference's cooperative
-// scheme, kernels/kernels/cuda/cooperative.cu:10-16, moved from global memory
-// to distributed shared memory).  Per layer and tile (dlr_lock/model.py:96-100
-// on folded weights, kernels/README.md:5-7):
+// Work split.  A cluster of CS = d/512 CTAs (1, 2, 4 or 8) walks all L layers
+// for one tile of 128 token rows; CTA `rank` owns columns [512*rank,
+// 512*rank+512) of the model width for BOTH contractions of a layer (K-stripe
+// of the V contraction, N-stripe of the U contraction - the reference's
+// cooperative scheme, kernels/kernels/cuda/cooperative.cu:10-16, moved from
+// global memory to distributed shared memory).  Per layer
+// (dlr_lock/model.py:96-100 on folded weights, kernels/README.md:5-7):
 //
-//   V:  z_part[128 x r]  = h[128 x 256] . V'[:, stripe]^T     tcgen05.mma, A from TMEM
+//   V:  z_part[128 x r]  = h[128 x 512] . V'[:, stripe]^T     tcgen05.mma, A from TMEM
 //   X:  z = sum over the cluster of z_part, sumsq likewise    DSMEM reduce-scatter by rows
 //       s = silu(z * rsqrt(sumsq/d + eps)) as bf16            DSMEM all-gather
-//   U:  dh[128 x 256]    = s[128 x r] . U'[stripe, :]^T       tcgen05.mma, A and B from smem
+//   U:  dh[128 x 512]    = s[128 x r] . U'[stripe, :]^T       tcgen05.mma, A and B from smem
 //       h += dh ; sumsq_part = sum h^2                        fused epilogue out of TMEM
 //
-// Two tiles per CTA.  The exchange X is a latency chain during which a tile
-// has no tensor work, so every CTA runs TWO independent pipelines, one per row
-// tile, each with its own weight ring, TMA warp, MMA warp and four epilogue
-// warps; whenever one tile waits on its exchange or epilogue the other tile's
-// contractions use the tensor core.  Two issuing warps are also what it takes
-// to keep the tensor core busy here: one thread issues a 128x128x16
-// tcgen05.mma only every ~130 cycles (measured), half of what the pipe can
-// execute.
+// On-chip residency.  256 tensor-memory columns hold the activation stripe
+// (128 x 512) as packed bf16 for the whole stack - it is the A operand of the V
+// contraction straight from TMEM - and the other 256 columns are two fp32
+// accumulators of 128 columns.  The activation is re-rounded to bf16 once per
+// layer, like every fused kernel of the reference (fp32 accumulation inside a
+// layer).  Partial z travels between CTAs as bf16 (summed in fp32): it is
+// rounded to bf16 right after the sum anyway, and the end-to-end error is
+// unchanged by it.
 //
-// On-chip residency.  Per tile, 128 tensor-memory columns hold the activation
-// stripe as packed bf16 (the A operand of the V contraction, straight from
-// TMEM) and 128 columns hold one fp32 accumulator (z, then the two dh chunks).
-// The activation is re-rounded to bf16 once per layer, like every fused kernel
-// of the reference (fp32 accumulation inside a layer).  Partial z travels
-// between CTAs as bf16 (summed in fp32): it is rounded once more to bf16 right
-// after the sum anyway, and the end-to-end error is unchanged by it.
+// Two MMA warps.  One thread can issue a 128xNx16 tcgen05.mma only about every
+// 125 cycles for any N <= 128 (measured), half of what the tensor pipe executes
+// at N = 128, while two issuing warps run side by side at full rate.  So the V
+// contraction is split along K over two warps into the two accumulators (the
+// halves are added when z is read out), and the four 128-column chunks of the
+// U contraction alternate between the two warps and accumulators.
 //
 // Exchange mechanics.  Every remote write is an asynchronous store
 // (st.async ... shared::cluster) whose bytes are counted on the RECEIVER's
 // mbarrier, so no fences or remote arrivals are needed: a row's partial z
-// (bf16) and its partial sum of squares go straight from the accumulator to
+// (bf16) and its partial sum of squares go straight from the accumulators to
 // the row's owner; the owner's s rows go to every CTA of the cluster, written
 // directly in the core-matrix layout the MMA reads (8 rows x 16 bytes
 // contiguous, no swizzle), which also makes each warp's stores contiguous.
 //
-// Roles.  Per tile: one warp streams 8 KB weight tiles (32 K-columns, 64-byte
-// swizzle) with TMA into that tile's ring, one lane of another warp issues the
-// tile's MMAs, four warps (one thread per row) run exchange and epilogue.
-// Warps 0/1 = TMA/MMA of tile A, 2/3 = TMA/MMA of tile B, 4-7 and 8-11 the two
-// epilogue groups.  All waits are bounded mbarrier waits; a wait that gives up
-// records a status word and every role drains to a common exit.
+// Roles.  Warp 0 streams 16 KB weight tiles with TMA into a deep ring and
+// never waits for activations; warps 1 and 2 issue MMAs; warps 4-11 (two
+// threads per row, each taking half of the columns) run exchange and epilogue.
+// All waits are bounded mbarrier waits; a wait that gives up records a status
+// word and every role drains to a common exit.
 #include <cstdlib>
 #include <cstring>
 
@@ -57,16 +55,15 @@ namespace dlr {
 namespace {
 
 constexpr int kRows = 128;
-constexpr int kStripe = 256;         // columns of the model width per CTA
-constexpr int kWK = 32;              // K columns per weight tile (one 64-byte swizzle span)
-constexpr int kVT = kStripe / kWK;   // V tiles per layer
+constexpr int kKT = 8;               // 64-column K tiles per stripe
+constexpr int kStripe = 64 * kKT;    // 512 columns per CTA
 constexpr int kNCH = kStripe / 128;  // 128-column output chunks per stripe
-constexpr int kStageBytes = 8192;
-constexpr int kMaxStages = 8;        // per tile
+constexpr int kStageBytes = 16384;
+constexpr int kMaxStages = 12;
 constexpr int kThreads = 384;
-constexpr uint32_t kTileCols = 256;  // tensor-memory columns per tile
-constexpr uint32_t kHOff = 0;        // packed bf16 activation: 128 columns
-constexpr uint32_t kAccOff = 128;    // fp32 accumulator: 128 columns
+constexpr int kEpi = 256;            // epilogue threads
+constexpr uint32_t kHOff = 0;        // packed bf16 activation: 256 columns
+constexpr uint32_t kAcc0 = 256;      // fp32 accumulator 0 (accumulator 1 follows at +128)
 
 struct ClusterParams {
     const __nv_bfloat16* x;
@@ -76,29 +73,26 @@ struct ClusterParams {
     int* status;
     unsigned int spin_limit;
     int stages;
-    int num_pairs;
-    int cs;
+    int num_tiles;
     unsigned long long* prof;   // optional per-CTA phase cycle counters (debug), or null
 };
 
 template <int R>
 struct CCfg {
+    static constexpr int KW = R < 64 ? R : 64;     // K columns per U weight tile
+    static constexpr int UK = R / KW;              // U weight tiles per 128-column chunk
     static constexpr int S_BYTES = kRows * R * 2;  // s tile (A operand of the U contraction)
     static constexpr int NCK = R / 8;              // 16-byte K chunks per row
     static constexpr int S_GROUP_BYTES = NCK * 128;          // one 8-row group of the s tile
-    static constexpr int R_GROUP_BYTES = (NCK + 1) * 128;    // same plus one chunk for the sums of squares
+    static constexpr int R_GROUP_BYTES = (NCK + 2) * 128;    // same plus two chunks for the sums of squares
     static constexpr int RECV_BYTES = (kRows / 8) * R_GROUP_BYTES;
-    static constexpr int V_TILE_BYTES = R * kWK * 2;         // R rows x 32 K-columns
-    static constexpr int U_TILE_BYTES = 128 * kWK * 2;       // 128 rows x 32 K-columns
-    static constexpr int UT = R / kWK;                       // U tiles per 128-column chunk
-    static constexpr uint32_t W_LAYOUT = 4u;                 // descriptor layout type: 64-byte swizzle
-    static constexpr uint32_t W_SBO = 8 * kWK * 2;           // bytes between 8-row groups of a weight tile
+    static constexpr int V_TILE_BYTES = R * 128;             // R rows x 64 K-columns, 128-byte swizzle
+    static constexpr int U_TILE_BYTES = 128 * KW * 2;        // 128 rows x KW K-columns
+    static constexpr uint32_t U_LAYOUT = KW == 64 ? 2u : 4u; // descriptor layout type (128- / 64-byte swizzle)
+    static constexpr uint32_t U_SBO = 8 * KW * 2;            // bytes between 8-row groups of a U tile
+    static constexpr int LOADS_PER_LAYER = kKT + kNCH * UK;
+    static constexpr int FIXED_BYTES = S_BYTES + RECV_BYTES + 1024 /*barriers*/ + 1024 /*alignment*/;
 };
-
-// per-tile shared-memory bytes besides the ring: the s tile and the receive buffer
-__host__ __device__ constexpr int tile_bytes(int R) {
-    return kRows * R * 2 + (kRows / 8) * (R / 8 + 1) * 128;
-}
 
 // K-major shared-memory operand descriptor: 8-row groups `sbo` bytes apart,
 // swizzle span 128 B (layout 2) or 64 B (layout 4); version 1.
@@ -109,6 +103,18 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t layout, u
     d |= uint64_t(sbo >> 4) << 32;
     d |= uint64_t(1) << 46;
     d |= uint64_t(layout) << 61;
+    return d;
+}
+
+// Shared-memory operand descriptor for the un-swizzled K-major layout: core
+// matrices of 8 rows x 16 bytes, `lbo` bytes apart along K, `sbo` bytes apart
+// along the rows.
+__device__ __forceinline__ uint64_t umma_desc_nosw(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= uint64_t((saddr & 0x3ffffu) >> 4);
+    d |= uint64_t(lbo >> 4) << 16;
+    d |= uint64_t(sbo >> 4) << 32;
+    d |= uint64_t(1) << 46;
     return d;
 }
 
@@ -134,7 +140,6 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8])
                  "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
                  : "memory");
 }
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // Asynchronous 16-byte store into a peer's (or this CTA's own) shared memory;
 // the 16 bytes are counted on the RECEIVER's mbarrier.  Both addresses are
@@ -145,22 +150,6 @@ __device__ __forceinline__ void st_async_v4(uint32_t dst_cluster, uint32_t a, ui
                      dst_cluster),
                  "r"(a), "r"(b), "r"(c), "r"(d), "r"(bar_cluster)
                  : "memory");
-}
-
-// Shared-memory operand descriptor for the un-swizzled K-major layout: core
-// matrices of 8 rows x 16 bytes, `lbo` bytes apart along K, `sbo` bytes apart
-// along the rows.
-__device__ __forceinline__ uint64_t umma_desc_nosw(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= uint64_t((saddr & 0x3ffffu) >> 4);
-    d |= uint64_t(lbo >> 4) << 16;
-    d |= uint64_t(sbo >> 4) << 32;
-    d |= uint64_t(1) << 46;
-    return d;
-}
-
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 
 #define DLR_CLK() (p.prof ? clock64() : 0ll)
@@ -184,14 +173,15 @@ struct Waiter {
     }
 };
 
-// Per-tile mbarriers.
-struct TileBars {
-    uint64_t z_full;       // MMA -> epilogue: partial z is in the accumulator
-    uint64_t recv_full;    // peers -> owner: all partials and sums of squares landed (byte count)
-    uint64_t s_full;       // peers -> MMA: the whole s tile landed (byte count)
-    uint64_t dh_full;      // MMA -> epilogue: a dh chunk is in the accumulator
-    uint64_t acc_empty;    // epilogue -> MMA: accumulator drained
-    uint64_t h_ready;      // epilogue -> MMA: activation stripe updated in tensor memory
+struct Bars {
+    uint64_t ring_full[kMaxStages];
+    uint64_t ring_empty[kMaxStages];
+    uint64_t z_full[2];      // MMA warp b -> epilogue: its half of the partial z is in accumulator b
+    uint64_t recv_full;      // peers -> owner: all partials and sums of squares landed (byte count)
+    uint64_t s_full;         // peers -> MMA warps: the whole s tile landed (byte count)
+    uint64_t dh_full[2];     // MMA warp b -> epilogue: a dh chunk is in accumulator b
+    uint64_t acc_empty[2];   // epilogue -> MMA warp b: accumulator b drained
+    uint64_t h_ready;        // epilogue -> MMA warps: activation stripe updated in tensor memory
 };
 
 template <int R, int CS>
@@ -201,17 +191,13 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
     using C = CCfg<R>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int S = p.stages;                       // ring stages per tile
+    const int S = p.stages;
     constexpr int rows_own = kRows / CS;
-    uint8_t* ring = smem;                         // [2][S][kStageBytes]
-    uint8_t* tile_mem = ring + size_t(2 * S) * kStageBytes;
-    // per tile: [s tile : S_BYTES][recv : RECV_BYTES]
-    constexpr int tile_stride = tile_bytes(R);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tile_mem + 2 * size_t(tile_stride));
-    uint64_t* ring_full = bars;                   // [2][kMaxStages]
-    uint64_t* ring_empty = bars + 2 * kMaxStages; // [2][kMaxStages]
-    TileBars* tb = reinterpret_cast<TileBars*>(bars + 4 * kMaxStages);   // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tb + 2);
+    uint8_t* ring = smem;
+    uint8_t* sbuf = ring + size_t(S) * kStageBytes;   // s tile, core-matrix layout
+    uint8_t* recv = sbuf + C::S_BYTES;                // [source][8-row group][chunk][row in group] x 16 B
+    Bars* bars = reinterpret_cast<Bars*>(recv + C::RECV_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -223,18 +209,18 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
     const Waiter w{abort_flag, p.spin_limit >> 2};
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < 2 * kMaxStages; ++s) {
-            mbar_init(smem_u32(&ring_full[s]), 1);
-            mbar_init(smem_u32(&ring_empty[s]), 1);
+        for (int s = 0; s < kMaxStages; ++s) {
+            mbar_init(smem_u32(&bars->ring_full[s]), 1);
+            mbar_init(smem_u32(&bars->ring_empty[s]), 1);
         }
-        for (int t = 0; t < 2; ++t) {
-            mbar_init(smem_u32(&tb[t].z_full), 1);
-            mbar_init(smem_u32(&tb[t].recv_full), 1);   // the local arrive that arms the byte count
-            mbar_init(smem_u32(&tb[t].s_full), 1);
-            mbar_init(smem_u32(&tb[t].dh_full), 1);
-            mbar_init(smem_u32(&tb[t].acc_empty), 128);
-            mbar_init(smem_u32(&tb[t].h_ready), 128);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars->z_full[b]), 1);
+            mbar_init(smem_u32(&bars->dh_full[b]), 1);
+            mbar_init(smem_u32(&bars->acc_empty[b]), kEpi);
         }
+        mbar_init(smem_u32(&bars->recv_full), 1);   // the local arrive that arms the byte count
+        mbar_init(smem_u32(&bars->s_full), 1);
+        mbar_init(smem_u32(&bars->h_ready), kEpi);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmV);
@@ -250,165 +236,161 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
     cluster_wait_acquire();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tile_s = smem_u32(tile_mem);
+    const uint32_t ring_s = smem_u32(ring);
+    const uint32_t sbuf_s = smem_u32(sbuf);
+    const uint32_t recv_s = smem_u32(recv);
 
     int err = 0;
     int err_layer = 0;
 
-    if (warp < 4) {
-        const int t = warp >> 1;                  // tile served by this warp
-        const uint32_t ring_s = smem_u32(ring) + uint32_t(t * S) * kStageBytes;
-        uint64_t* rfull = ring_full + t * kMaxStages;
-        uint64_t* rempty = ring_empty + t * kMaxStages;
-        if ((warp & 1) == 0) {
-            // =============================== TMA producer of tile t =====================
-            if (lane == 0) {
-                uint32_t n = 0;
-                long long pw = 0;
-                for (int pair = cluster_id; pair < p.num_pairs && !err; pair += num_clusters) {
-                    for (int l = 0; l < p.L && !err; ++l) {
-                        for (int i = 0; i < kVT + kNCH * C::UT; ++i, ++n) {
-                            const uint32_t st = n % uint32_t(S);
-                            const uint32_t ph = (n / uint32_t(S)) & 1u;
-                            const long long t0 = DLR_CLK();
-                            if (!w.cta(smem_u32(&rempty[st]), ph ^ 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; err_layer = l; break; }
-                            pw += DLR_CLK() - t0;
-                            const uint32_t bar = smem_u32(&rfull[st]);
-                            const uint32_t dst = ring_s + st * kStageBytes;
-                            if (i < kVT) {
-                                mbar_arrive_expect_tx(bar, C::V_TILE_BYTES);
-                                tma_load_2d(dst, &tmV, stripe0 + kWK * i, l * R, bar);
-                                // pull the same tile of the NEXT layer into L2 (tile A's producer only:
-                                // both tiles read the same weights)
-                                if (t == 0 && l + 1 < p.L) tma_prefetch_2d(&tmV, stripe0 + kWK * i, (l + 1) * R);
-                            } else {
-                                const int j = i - kVT;
-                                const int nc = j / C::UT, kq = j % C::UT;
-                                mbar_arrive_expect_tx(bar, C::U_TILE_BYTES);
-                                tma_load_2d(dst, &tmU, kq * kWK, l * p.d + stripe0 + 128 * nc, bar);
-                                if (t == 0 && l + 1 < p.L) tma_prefetch_2d(&tmU, kq * kWK, (l + 1) * p.d + stripe0 + 128 * nc);
-                            }
+    if (warp == 0) {
+        // =============================== TMA producer ===============================
+        if (lane == 0) {
+            uint32_t n = 0;
+            long long pw = 0;
+            for (int tile = cluster_id; tile < p.num_tiles && !err; tile += num_clusters) {
+                for (int l = 0; l < p.L && !err; ++l) {
+                    for (int i = 0; i < C::LOADS_PER_LAYER; ++i, ++n) {
+                        const uint32_t st = n % uint32_t(S);
+                        const uint32_t ph = (n / uint32_t(S)) & 1u;
+                        const long long t0 = DLR_CLK();
+                        if (!w.cta(smem_u32(&bars->ring_empty[st]), ph ^ 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; err_layer = l; break; }
+                        pw += DLR_CLK() - t0;
+                        const uint32_t bar = smem_u32(&bars->ring_full[st]);
+                        const uint32_t dst = ring_s + st * kStageBytes;
+                        if (i < kKT) {
+                            mbar_arrive_expect_tx(bar, C::V_TILE_BYTES);
+                            tma_load_2d(dst, &tmV, stripe0 + 64 * i, l * R, bar);
+                        } else {
+                            const int j = i - kKT;
+                            const int nc = j / C::UK, kh = j % C::UK;
+                            mbar_arrive_expect_tx(bar, C::U_TILE_BYTES);
+                            tma_load_2d(dst, &tmU, kh * C::KW, l * p.d + stripe0 + 128 * nc, bar);
                         }
-                    }
-                }
-                if (p.prof) p.prof[(blockIdx.x * 6 + t) * 16 + 0] = (unsigned long long)pw;
-                if (err) {
-                    // copies issued before giving up still land in this CTA's ring:
-                    // wait (bounded) for them before leaving.
-                    for (uint32_t back = 1; back <= uint32_t(S) && back <= n; ++back) {
-                        const uint32_t m = n - back;
-                        mbar_wait(smem_u32(&rfull[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, p.spin_limit >> 6);
                     }
                 }
             }
-        } else {
-            // =============================== MMA issuer of tile t =======================
-            if (lane == 0) {
-                const uint32_t idesc_v = umma_idesc_bf16(128, R);
-                const uint32_t idesc_u = umma_idesc_bf16(128, 128);
-                const uint32_t tcol = tmem_base + uint32_t(t) * kTileCols;
-                const uint32_t sb = tile_s + uint32_t(t) * uint32_t(tile_stride);
-                uint32_t n = 0;                      // ring position of the next weight tile
-                uint32_t c_h = 0, c_s = 0, c_e = 0;
-                long long m[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                const long long mstart = DLR_CLK();
-                for (int pair = cluster_id; pair < p.num_pairs && !err; pair += num_clusters) {
-                    for (int l = 0; l < p.L && !err; ++l) {
-                        err_layer = l;
-                        // ---- V contraction: accumulator = h . V'^T over the 8 K tiles of the stripe
-                        long long t0 = DLR_CLK();
-                        if (!w.cta(smem_u32(&tb[t].h_ready), c_h & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        ++c_h;
-                        tc_fence_after();
-                        long long t1 = DLR_CLK();
-                        m[0] += t1 - t0;
-                        for (int kt = 0; kt < kVT && !err; ++kt, ++n) {
-                            const uint32_t st = n % uint32_t(S);
-                            const long long r0 = DLR_CLK();
-                            if (!w.cta(smem_u32(&rfull[st]), (n / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
-                            m[4] += DLR_CLK() - r0;
-                            tc_fence_after();
-                            const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, C::W_LAYOUT, C::W_SBO);
-#pragma unroll
-                            for (int k = 0; k < kWK / 16; ++k)
-                                umma_ts(tcol + kAccOff, tcol + kHOff + uint32_t(kt * (kWK / 2) + k * 8), bdesc + uint64_t(2 * k),
-                                        idesc_v, (kt | k) ? 1u : 0u);
-                            umma_commit(smem_u32(&rempty[st]));
-                        }
-                        if (err) break;
-                        umma_commit(smem_u32(&tb[t].z_full));
-                        t0 = DLR_CLK();
-                        m[1] += t0 - t1;
-                        // ---- U contraction: two 128-column chunks through the one accumulator
-                        if (!w.cluster(smem_u32(&tb[t].s_full), c_s & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        ++c_s;
-                        tc_fence_after();
-                        t1 = DLR_CLK();
-                        m[2] += t1 - t0;
-                        for (int nc = 0; nc < kNCH && !err; ++nc) {
-                            const long long a0 = DLR_CLK();
-                            if (!w.cta(smem_u32(&tb[t].acc_empty), c_e & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                            ++c_e;
-                            tc_fence_after();
-                            m[6] += DLR_CLK() - a0;
-                            for (int kq = 0; kq < C::UT && !err; ++kq, ++n) {
-                                const uint32_t st = n % uint32_t(S);
-                                const long long r0 = DLR_CLK();
-                                if (!w.cta(smem_u32(&rfull[st]), (n / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
-                                m[5] += DLR_CLK() - r0;
-                                tc_fence_after();
-                                const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, C::W_LAYOUT, C::W_SBO);
-#pragma unroll
-                                for (int k = 0; k < kWK / 16; ++k) {
-                                    // K step ks of the s tile: two 16-byte chunks, 128 bytes apart
-                                    const int ks = kq * (kWK / 16) + k;
-                                    const uint64_t adesc = umma_desc_nosw(sb + uint32_t(ks) * 256u, 128u, C::S_GROUP_BYTES);
-                                    umma_ss(tcol + kAccOff, adesc, bdesc + uint64_t(2 * k), idesc_u, (kq | k) ? 1u : 0u);
-                                }
-                                umma_commit(smem_u32(&rempty[st]));
-                            }
-                            if (err) break;
-                            umma_commit(smem_u32(&tb[t].dh_full));
-                        }
-                        m[3] += DLR_CLK() - t1;
-                    }
-                }
-                if (p.prof) {
-                    m[7] = DLR_CLK() - mstart;
-                    for (int k = 0; k < 8; ++k) p.prof[(blockIdx.x * 6 + 2 + t) * 16 + k] = (unsigned long long)m[k];
+            if (p.prof) p.prof[(blockIdx.x * 4 + 0) * 16 + 0] = (unsigned long long)pw;
+            if (err) {
+                // copies issued before giving up still land in this CTA's ring:
+                // wait (bounded) for them before leaving.
+                for (uint32_t back = 1; back <= uint32_t(S) && back <= n; ++back) {
+                    const uint32_t m = n - back;
+                    mbar_wait(smem_u32(&bars->ring_full[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, p.spin_limit >> 6);
                 }
             }
         }
-    } else {
+    } else if (warp == 1 || warp == 2) {
+        // =============================== MMA issuer b ===============================
+        // b = 0: K tiles 0-3 of the V contraction, U chunks 0 and 2, accumulator 0
+        // b = 1: K tiles 4-7,                       U chunks 1 and 3, accumulator 1
+        if (lane == 0) {
+            const int b = warp - 1;
+            const uint32_t acc = tmem_base + kAcc0 + uint32_t(b) * 128u;
+            const uint32_t idesc_v = umma_idesc_bf16(128, R);
+            const uint32_t idesc_u = umma_idesc_bf16(128, 128);
+            uint32_t nb = 0;                     // ring position of this layer's first weight tile
+            uint32_t c_h = 0, c_s = 0, c_e = 0;
+            long long m[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const long long mstart = DLR_CLK();
+            for (int tile = cluster_id; tile < p.num_tiles && !err; tile += num_clusters) {
+                for (int l = 0; l < p.L && !err; ++l, nb += C::LOADS_PER_LAYER) {
+                    err_layer = l;
+                    long long t0 = DLR_CLK();
+                    if (!w.cta(smem_u32(&bars->h_ready), c_h & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    ++c_h;
+                    tc_fence_after();
+                    long long t1 = DLR_CLK();
+                    m[0] += t1 - t0;
+                    // ---- this warp's half of the V contraction
+                    for (int kk = 0; kk < kKT / 2 && !err; ++kk) {
+                        const int kt = b * (kKT / 2) + kk;
+                        const uint32_t idx = nb + uint32_t(kt);
+                        const uint32_t st = idx % uint32_t(S);
+                        const long long r0 = DLR_CLK();
+                        if (!w.cta(smem_u32(&bars->ring_full[st]), (idx / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                        m[4] += DLR_CLK() - r0;
+                        tc_fence_after();
+                        const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, 2u, 1024u);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma_ts(acc, tmem_base + kHOff + uint32_t(kt * 32 + k * 8), bdesc + uint64_t(2 * k), idesc_v,
+                                    (kk | k) ? 1u : 0u);
+                        umma_commit(smem_u32(&bars->ring_empty[st]));
+                    }
+                    if (err) break;
+                    umma_commit(smem_u32(&bars->z_full[b]));
+                    t0 = DLR_CLK();
+                    m[1] += t0 - t1;
+                    // ---- this warp's two chunks of the U contraction
+                    if (!w.cluster(smem_u32(&bars->s_full), c_s & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    ++c_s;
+                    tc_fence_after();
+                    t1 = DLR_CLK();
+                    m[2] += t1 - t0;
+                    for (int j = 0; j < kNCH / 2 && !err; ++j) {
+                        const int nc = b + 2 * j;
+                        const long long a0 = DLR_CLK();
+                        if (!w.cta(smem_u32(&bars->acc_empty[b]), c_e & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        ++c_e;
+                        tc_fence_after();
+                        m[6] += DLR_CLK() - a0;
+                        for (int kh = 0; kh < C::UK && !err; ++kh) {
+                            const uint32_t idx = nb + uint32_t(kKT + nc * C::UK + kh);
+                            const uint32_t st = idx % uint32_t(S);
+                            const long long r0 = DLR_CLK();
+                            if (!w.cta(smem_u32(&bars->ring_full[st]), (idx / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                            m[5] += DLR_CLK() - r0;
+                            tc_fence_after();
+                            const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, C::U_LAYOUT, C::U_SBO);
+#pragma unroll
+                            for (int k = 0; k < C::KW / 16; ++k) {
+                                // K step ks of the s tile: two 16-byte chunks, 128 bytes apart
+                                const int ks = kh * (C::KW / 16) + k;
+                                const uint64_t adesc = umma_desc_nosw(sbuf_s + uint32_t(ks) * 256u, 128u, C::S_GROUP_BYTES);
+                                umma_ss(acc, adesc, bdesc + uint64_t(2 * k), idesc_u, (kh | k) ? 1u : 0u);
+                            }
+                            umma_commit(smem_u32(&bars->ring_empty[st]));
+                        }
+                        if (err) break;
+                        umma_commit(smem_u32(&bars->dh_full[b]));
+                    }
+                    m[3] += DLR_CLK() - t1;
+                }
+            }
+            if (p.prof) {
+                m[7] = DLR_CLK() - mstart;
+                for (int k = 0; k < 8; ++k) p.prof[(blockIdx.x * 4 + 1 + b) * 16 + k] = (unsigned long long)m[k];
+            }
+        }
+    } else if (warp >= 4) {
         // =============================== epilogue warps =============================
-        const int t = (warp - 4) >> 2;               // tile served by this warp group
-        const int gw = (warp - 4) & 3;               // warp inside the group
-        const int gt = gw * 32 + lane;               // thread inside the group, 0..127
+        // Two threads per row: thread (row er, half hh) owns the columns of half hh of
+        // z, of every dh chunk and of the activation stripe.
+        const int et = threadIdx.x - 128;            // 0..255
+        const int hh = (warp - 4) >> 2;              // column half
         const int q = warp & 3;                      // tensor-memory lane quadrant of this warp
-        const int er = 32 * q + lane;                // row of the tile this thread owns
-        const uint32_t tl = tmem_base + uint32_t(t) * kTileCols + (uint32_t(32 * q) << 16);
-        const uint32_t sbuf_s = tile_s + uint32_t(t) * uint32_t(tile_stride);
-        const uint32_t recv_s = sbuf_s + C::S_BYTES;
-        const uint8_t* recv_g = tile_mem + size_t(t) * tile_stride + C::S_BYTES;
-        TileBars& B = tb[t];
+        const int er = 32 * q + lane;                // row of the tile
+        const uint32_t tl = tmem_base + (uint32_t(32 * q) << 16);
         const int owner = er / rows_own;
         const int lr = er % rows_own;
-        constexpr int groups_own = rows_own / 8;         // 8-row groups per owner
+        constexpr int groups_own = rows_own / 8;     // 8-row groups per owner
         constexpr uint32_t src_bytes = uint32_t(groups_own) * C::R_GROUP_BYTES;   // one source's block in recv
-        constexpr int items = rows_own * C::NCK / 128;   // 16-byte chunks of s per thread in the reduce
-        uint32_t c_z = 0, c_recv = 0, c_dh = 0;
+        constexpr int items = rows_own * C::NCK / kEpi;   // 16-byte chunks of s per thread in the reduce
+        constexpr int NZ = R / 2;                    // columns of z per thread
+        uint32_t c_z = 0, c_recv = 0, c_dh[2] = {0, 0};
         long long e[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const long long estart = DLR_CLK();
 
-        for (int pair = cluster_id; pair < p.num_pairs && !err; pair += num_clusters) {
-            const int grow = (2 * pair + t) * kRows + er;
+        for (int tile = cluster_id; tile < p.num_tiles && !err; tile += num_clusters) {
+            const int grow = tile * kRows + er;
             const bool valid = grow < p.M;
             const long long x0 = DLR_CLK();
-            const __nv_bfloat16* xrow = p.x + size_t(valid ? grow : 0) * p.d + stripe0;
+            const __nv_bfloat16* xrow = p.x + size_t(valid ? grow : 0) * p.d + stripe0 + 256 * hh;
             float ssq = 0.f;
-            // ---- input stripe -> tensor memory (packed bf16), partial sum of squares
+            // ---- input half-stripe -> tensor memory (packed bf16), partial sum of squares
 #pragma unroll 4
-            for (int c = 0; c < kStripe / 16; ++c) {
+            for (int c = 0; c < 16; ++c) {
                 uint32_t v[8];
                 if (valid) {
                     const uint4 a = __ldg(reinterpret_cast<const uint4*>(xrow + 16 * c));
@@ -423,61 +405,68 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                     const float lo = bf16lo_to_f(v[j]), hi = bf16hi_to_f(v[j]);
                     ssq += lo * lo + hi * hi;
                 }
-                tmem_st8(tl + kHOff + uint32_t(8 * c), v);
+                tmem_st8(tl + kHOff + uint32_t(128 * hh + 8 * c), v);
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(smem_u32(&B.h_ready));
+            mbar_arrive(smem_u32(&bars->h_ready));
             e[6] += DLR_CLK() - x0;
 
             for (int l = 0; l < p.L && !err; ++l) {
                 err_layer = l;
                 long long t0 = DLR_CLK();
-                // ---- partial z of this row: accumulator -> bf16 -> the row's owner
-                if (!__all_sync(0xffffffffu, w.cta(smem_u32(&B.z_full), c_z & 1u))) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                // ---- partial z of this row (both K halves added) -> bf16 -> the row's owner
+                bool ok = w.cta(smem_u32(&bars->z_full[0]), c_z & 1u);
+                ok = ok && w.cta(smem_u32(&bars->z_full[1]), c_z & 1u);
+                if (!__all_sync(0xffffffffu, ok)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                 ++c_z;
                 tc_fence_after();
                 long long t1 = DLR_CLK();
                 e[0] += t1 - t0;
-                if (gt == 0) mbar_arrive_expect_tx(smem_u32(&B.recv_full), C::RECV_BYTES);   // arm this layer's receive
+                if (et == 0) mbar_arrive_expect_tx(smem_u32(&bars->recv_full), C::RECV_BYTES);   // arm this layer's receive
                 {
-                    // this row's slot in its owner's receive buffer: [source][8-row group][chunk][row in group]
+                    // this row's slot in its owner's receive buffer
                     const uint32_t dst = mapa(recv_s + uint32_t(rank) * src_bytes + uint32_t(lr >> 3) * C::R_GROUP_BYTES +
                                                   uint32_t(lr & 7) * 16u, uint32_t(owner));
-                    const uint32_t rbar = mapa(smem_u32(&B.recv_full), uint32_t(owner));
+                    const uint32_t rbar = mapa(smem_u32(&bars->recv_full), uint32_t(owner));
 #pragma unroll
-                    for (int c = 0; c < R / 32; ++c) {
-                        uint32_t v[32];
-                        tmem_ld32(tl + kAccOff + uint32_t(32 * c), v);
+                    for (int c = 0; c < NZ / 16; ++c) {
+                        uint32_t v0[16], v1[16];
+                        tmem_ld16(tl + kAcc0 + uint32_t(NZ * hh + 16 * c), v0);
+                        tmem_ld16(tl + kAcc0 + 128u + uint32_t(NZ * hh + 16 * c), v1);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            st_async_v4(dst + uint32_t(4 * c + j) * 128u,
-                                        pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1])),
-                                        pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
-                                        pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
-                                        pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])), rbar);
+                        for (int j = 0; j < 2; ++j) {
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                pk[i] = pack_bf16x2(__uint_as_float(v0[8 * j + 2 * i]) + __uint_as_float(v1[8 * j + 2 * i]),
+                                                    __uint_as_float(v0[8 * j + 2 * i + 1]) + __uint_as_float(v1[8 * j + 2 * i + 1]));
+                            const int chunk = (NZ * hh + 16 * c + 8 * j) / 8;
+                            st_async_v4(dst + uint32_t(chunk) * 128u, pk[0], pk[1], pk[2], pk[3], rbar);
+                        }
                     }
-                    st_async_v4(dst + uint32_t(C::NCK) * 128u, __float_as_uint(ssq), 0u, 0u, 0u, rbar);
+                    st_async_v4(dst + uint32_t(C::NCK + hh) * 128u, __float_as_uint(ssq), 0u, 0u, 0u, rbar);
                 }
                 tc_fence_before();
-                mbar_arrive(smem_u32(&B.acc_empty));     // z has left the accumulator
+                mbar_arrive(smem_u32(&bars->acc_empty[0]));   // z has left both accumulators
+                mbar_arrive(smem_u32(&bars->acc_empty[1]));
                 t0 = DLR_CLK();
                 e[1] += t0 - t1;
 
                 // ---- owner: sum the CS partials of its rows, normalise, SiLU, all-gather
-                if (!__all_sync(0xffffffffu, w.cluster(smem_u32(&B.recv_full), c_recv & 1u))) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                if (!__all_sync(0xffffffffu, w.cluster(smem_u32(&bars->recv_full), c_recv & 1u))) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                 ++c_recv;
                 t1 = DLR_CLK();
                 e[2] += t1 - t0;
-                if (gt == 0) mbar_arrive_expect_tx(smem_u32(&B.s_full), C::S_BYTES);      // arm this layer's s tile
+                if (et == 0) mbar_arrive_expect_tx(smem_u32(&bars->s_full), C::S_BYTES);      // arm this layer's s tile
 #pragma unroll
                 for (int it = 0; it < items; ++it) {
-                    const int i = gt + 128 * it;
+                    const int i = et + kEpi * it;
                     const int r8 = i & 7;
                     const int c = (i >> 3) % C::NCK;
                     const int gl = i / R;                 // 8-row group inside this owner's rows
-                    const uint8_t* base = recv_g + size_t(gl) * C::R_GROUP_BYTES + r8 * 16;
+                    const uint8_t* base = recv + size_t(gl) * C::R_GROUP_BYTES + r8 * 16;
                     float tot = 0.f;
                     float a[8];
 #pragma unroll
@@ -486,7 +475,8 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                     for (int src = 0; src < CS; ++src) {
                         const uint8_t* bp = base + size_t(src) * src_bytes;
                         const uint4 u = *reinterpret_cast<const uint4*>(bp + c * 128);
-                        tot += *reinterpret_cast<const float*>(bp + C::NCK * 128);
+                        tot += *reinterpret_cast<const float*>(bp + C::NCK * 128) +
+                               *reinterpret_cast<const float*>(bp + (C::NCK + 1) * 128);
                         a[0] += bf16lo_to_f(u.x); a[1] += bf16hi_to_f(u.x);
                         a[2] += bf16lo_to_f(u.y); a[3] += bf16hi_to_f(u.y);
                         a[4] += bf16lo_to_f(u.z); a[5] += bf16hi_to_f(u.z);
@@ -503,7 +493,7 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
 #pragma unroll
                     for (int dc = 0; dc < CS; ++dc)
                         st_async_v4(mapa(sbuf_s + soff, uint32_t(dc)), p0, p1, p2, p3,
-                                    mapa(smem_u32(&B.s_full), uint32_t(dc)));
+                                    mapa(smem_u32(&bars->s_full), uint32_t(dc)));
                 }
                 t0 = DLR_CLK();
                 e[3] += t0 - t1;
@@ -511,29 +501,44 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                 // ---- fused epilogue of the U contraction: h += dh, new sum of squares
                 float ssq_new = 0.f;
                 for (int nc = 0; nc < kNCH && !err; ++nc) {
+                    const int b = nc & 1;
                     const long long d0 = DLR_CLK();
-                    if (!__all_sync(0xffffffffu, w.cta(smem_u32(&B.dh_full), c_dh & 1u))) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                    ++c_dh;
+                    if (!__all_sync(0xffffffffu, w.cta(smem_u32(&bars->dh_full[b]), c_dh[b] & 1u))) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    ++c_dh[b];
                     tc_fence_after();
                     e[4] += DLR_CLK() - d0;
-#pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t dh[32], hp[16];
-                        tmem_ld32(tl + kAccOff + uint32_t(32 * c), dh);
-                        tmem_ld16(tl + kHOff + uint32_t(64 * nc + 16 * c), hp);
+                    const uint32_t acc = tl + kAcc0 + uint32_t(b) * 128u + uint32_t(64 * hh);
+                    const uint32_t hcol = tl + kHOff + uint32_t(64 * nc + 32 * hh);
+                    {
+                        // both 32-column halves are fetched before either is processed: one
+                        // tensor-memory round trip per chunk instead of two
+                        uint32_t dh0[32], dh1[32], hp0[16], hp1[16];
+                        tmem_ld32(acc, dh0);
+                        tmem_ld16(hcol, hp0);
+                        tmem_ld32(acc + 32u, dh1);
+                        tmem_ld16(hcol + 16u, hp1);
                         tmem_wait_ld();
+                        if (nc + 2 < kNCH) {
+                            // the dh values are in registers: the accumulator can take the next chunk
+                            tc_fence_before();
+                            mbar_arrive(smem_u32(&bars->acc_empty[b]));
+                        }
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const float lo = bf16lo_to_f(hp[j]) + __uint_as_float(dh[2 * j]);
-                            const float hi = bf16hi_to_f(hp[j]) + __uint_as_float(dh[2 * j + 1]);
+                            const float lo = bf16lo_to_f(hp0[j]) + __uint_as_float(dh0[2 * j]);
+                            const float hi = bf16hi_to_f(hp0[j]) + __uint_as_float(dh0[2 * j + 1]);
                             ssq_new += lo * lo + hi * hi;
-                            hp[j] = pack_bf16x2(lo, hi);
+                            hp0[j] = pack_bf16x2(lo, hi);
                         }
-                        tmem_st16(tl + kHOff + uint32_t(64 * nc + 16 * c), hp);
-                    }
-                    if (nc + 1 < kNCH) {
-                        tc_fence_before();
-                        mbar_arrive(smem_u32(&B.acc_empty));
+                        tmem_st16(hcol, hp0);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float lo = bf16lo_to_f(hp1[j]) + __uint_as_float(dh1[2 * j]);
+                            const float hi = bf16hi_to_f(hp1[j]) + __uint_as_float(dh1[2 * j + 1]);
+                            ssq_new += lo * lo + hi * hi;
+                            hp1[j] = pack_bf16x2(lo, hi);
+                        }
+                        tmem_st16(hcol + 16u, hp1);
                     }
                 }
                 if (err) break;
@@ -541,17 +546,17 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                 tmem_wait_st();
                 if (l + 1 < p.L) {
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&B.h_ready));
+                    mbar_arrive(smem_u32(&bars->h_ready));
                 }
                 e[5] += DLR_CLK() - t0;
             }
             if (err) break;
-            // ---- final activation stripe -> global
-            __nv_bfloat16* yrow = p.y + size_t(valid ? grow : 0) * p.d + stripe0;
+            // ---- final activation half-stripe -> global
+            __nv_bfloat16* yrow = p.y + size_t(valid ? grow : 0) * p.d + stripe0 + 256 * hh;
 #pragma unroll 4
-            for (int c = 0; c < kStripe / 16; ++c) {
+            for (int c = 0; c < 16; ++c) {
                 uint32_t v[8];
-                tmem_ld8(tl + kHOff + uint32_t(8 * c), v);
+                tmem_ld8(tl + kHOff + uint32_t(128 * hh + 8 * c), v);
                 tmem_wait_ld();
                 if (valid) {
                     *reinterpret_cast<uint4*>(yrow + 16 * c) = make_uint4(v[0], v[1], v[2], v[3]);
@@ -559,9 +564,9 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                 }
             }
         }
-        if (p.prof && gt == 0) {
+        if (p.prof && et == 0) {
             e[7] = DLR_CLK() - estart;
-            for (int k = 0; k < 8; ++k) p.prof[(blockIdx.x * 6 + 4 + t) * 16 + k] = (unsigned long long)e[k];
+            for (int k = 0; k < 8; ++k) p.prof[(blockIdx.x * 4 + 3) * 16 + k] = (unsigned long long)e[k];
         }
     }
 
@@ -587,25 +592,21 @@ int launch_cluster(void* enc, const void* x, void* y, const void* Vp, const void
                    dlrb200_plan* plan_only, unsigned long long* prof) {
     using C = CCfg<R>;
     auto kern = dlr_cluster_kernel<R, CS>;
-    const int cs = CS;
     if (d != CS * kStripe) return DLRB200_ERR_UNSUPPORTED_SHAPE;
-    const int fixed = 2 * tile_bytes(R) + 1024 /*barriers*/ + 1024 /*alignment*/;
-    int stages = (smem_optin - fixed) / (2 * kStageBytes);      // per tile
+    int stages = (smem_optin - C::FIXED_BYTES) / kStageBytes;
     if (stages > kMaxStages) stages = kMaxStages;
-    if (stages < 3) return DLRB200_ERR_UNSUPPORTED_SHAPE;
-    const int smem = 2 * stages * kStageBytes + fixed;
+    // the two MMA warps read the two halves of a layer's V tiles at the same time
+    if (stages < kKT + 1) return DLRB200_ERR_UNSUPPORTED_SHAPE;
+    const int smem = stages * kStageBytes + C::FIXED_BYTES;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return DLRB200_ERR_CUDA;
-    if (cs > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
         return DLRB200_ERR_CUDA;
 
     const int num_tiles = (M + kRows - 1) / kRows;
-    const int num_pairs = (num_tiles + 1) / 2;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cs;
+    attr[0].val.clusterDim.x = CS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.blockDim = dim3(kThreads);
@@ -613,18 +614,18 @@ int launch_cluster(void* enc, const void* x, void* y, const void* Vp, const void
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cfg.gridDim = dim3(cs * (num_sms / cs));
+    cfg.gridDim = dim3(CS * (num_sms / CS));
     int max_clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess) return DLRB200_ERR_CUDA;
     if (max_clusters < 1) return DLRB200_ERR_OCCUPANCY;
-    const int clusters = num_pairs < max_clusters ? num_pairs : max_clusters;
-    cfg.gridDim = dim3(cs * clusters);
+    const int clusters = num_tiles < max_clusters ? num_tiles : max_clusters;
+    cfg.gridDim = dim3(CS * clusters);
     if (plan_only) {
         plan_only->path = DLRB200_PATH_CLUSTER;
-        plan_only->grid = cs * clusters;
-        plan_only->cluster = cs;
+        plan_only->grid = CS * clusters;
+        plan_only->cluster = CS;
         plan_only->stripe_cols = kStripe;
-        plan_only->rows_per_pass = 2 * kRows;
+        plan_only->rows_per_pass = kRows;
         plan_only->passes = 1;
         plan_only->stages = stages;
         plan_only->smem_bytes = size_t(smem);
@@ -638,15 +639,22 @@ int launch_cluster(void* enc, const void* x, void* y, const void* Vp, const void
     p.status = status_dev;
     p.spin_limit = spin_limit;
     p.stages = stages;
-    p.num_pairs = num_pairs;
-    p.cs = cs;
+    p.num_tiles = num_tiles;
     p.prof = prof;
     CUtensorMap tmV, tmU;
-    if (!encode_2d_bf16(enc, &tmV, Vp, uint64_t(d), uint64_t(L) * R, kWK, R, kWK * 2) ||
-        !encode_2d_bf16(enc, &tmU, Up, uint64_t(R), uint64_t(L) * d, kWK, 128, kWK * 2))
+    if (!encode_2d_bf16(enc, &tmV, Vp, uint64_t(d), uint64_t(L) * R, 64, R, 128) ||
+        !encode_2d_bf16(enc, &tmU, Up, uint64_t(R), uint64_t(L) * d, C::KW, 128, C::KW * 2))
         return DLRB200_ERR_CUDA;
     const cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, tmV, tmU, p);
     return ce == cudaSuccess ? DLRB200_OK : DLRB200_ERR_CUDA;
+}
+
+// (r, cluster size) pairs that are built; the reduce needs r >= 16 * CS so that
+// every epilogue thread owns at least one 16-byte chunk of s.
+bool combo_ok(int r, int cs) {
+    if (!(cs == 1 || cs == 2 || cs == 4 || cs == 8)) return false;
+    if (!(r == 32 || r == 64 || r == 128)) return false;
+    return r >= 16 * cs;
 }
 
 int dispatch(void* enc, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r, int L, float eps,
@@ -656,19 +664,22 @@ int dispatch(void* enc, const void* x, void* y, const void* Vp, const void* Up, 
     if (r == RR && d == CC * kStripe)                                                                             \
         return launch_cluster<RR, CC>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin,   \
                                       spin_limit, plan_only, prof);
-    DLR_CASE(32, 4)
+    DLR_CASE(32, 1)
+    DLR_CASE(32, 2)
+    DLR_CASE(64, 1)
+    DLR_CASE(64, 2)
     DLR_CASE(64, 4)
-    DLR_CASE(64, 8)
+    DLR_CASE(128, 1)
+    DLR_CASE(128, 2)
     DLR_CASE(128, 4)
     DLR_CASE(128, 8)
-    DLR_CASE(128, 16)
 #undef DLR_CASE
     return DLRB200_ERR_UNSUPPORTED_SHAPE;
 }
 
 // Debug aid: with DLRB200_PROFILE=1 in the environment every CTA writes cycle
-// counts of its phases (6 roles x 16 counters) at offset 256 of the workspace.
-constexpr size_t kProfBytes = 256 + size_t(256) * 6 * 16 * 8;
+// counts of its phases (4 roles x 16 counters) at offset 256 of the workspace.
+constexpr size_t kProfBytes = 256 + size_t(256) * 4 * 16 * 8;
 
 bool profiling() {
     const char* v = std::getenv("DLRB200_PROFILE");
@@ -680,10 +691,7 @@ bool profiling() {
 bool cluster_supported(int d, int r, int L) {
     (void)L;
     if (d % kStripe != 0) return false;
-    const int cs = d / kStripe;
-    if (!(cs == 4 || cs == 8 || cs == 16)) return false;
-    if (!(r == 32 || r == 64 || r == 128)) return false;
-    return r / cs >= 8;
+    return combo_ok(r, d / kStripe);
 }
 
 size_t cluster_workspace_bytes(int, int, int, int) { return profiling() ? kProfBytes : 0; }

@@ -202,8 +202,9 @@ def _cluster_case(D, d, r, L, M, seed, alpha, jitter=0.0):
     return p, x, y, Vf, Uf
 
 
-@pytest.mark.parametrize("d,r,M", [(1024, 32, 130), (1024, 64, 65), (2048, 64, 384), (2048, 128, 200),
-                                   (4096, 128, 129), (4096, 128, 700), (1024, 32, 1100)])
+@pytest.mark.parametrize("d,r,M", [(512, 32, 128), (512, 64, 65), (512, 128, 200), (1024, 32, 130), (1024, 64, 65),
+                                   (2048, 64, 384), (2048, 128, 200), (4096, 128, 129), (4096, 128, 700),
+                                   (1024, 32, 1100)])
 def test_cluster_path_shapes(D, d, r, M):
     p, x, y, Vf, Uf = _cluster_case(D, d, r, 5, M, seed=d + r + M, alpha=1.0, jitter=0.1)
     # same algebra with the activation re-rounded to bf16 after every layer (the bf16
