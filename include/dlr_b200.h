@@ -58,6 +58,7 @@ extern "C" {
 #define DLRB200_ERR_CUDA 6
 #define DLRB200_ERR_TIMEOUT_BARRIER 7
 #define DLRB200_ERR_TIMEOUT_COPY 8
+#define DLRB200_ERR_STATIC_LIMIT 9 /* only from dlrb200_forward_static: request larger than its built-in scratch */
 
 /* Execution paths reported by dlrb200_query. */
 #define DLRB200_PATH_STRIPED 1 /* small batch: width-striped CTAs, weight streaming, mma.sync */
@@ -130,6 +131,31 @@ DLRB200_API int dlrb200_fold_weights(const void* V, const void* U, const void* g
 /* Transpose a stack of L bf16 matrices (rows, cols) -> (cols, rows) on the
  * device; used to accept the reference CUDA convention Us (L, r, d). */
 DLRB200_API int dlrb200_transpose_stack(const void* src, void* dst, int L, int rows, int cols, void* stream);
+
+/* Small-batch forward for hosts that must not allocate device memory while
+ * serving (no counterpart in the reference, whose entry points allocate their
+ * scratch with torch on every call).  Think of a decode server whose memory
+ * budget is fixed at start-up, or a bare C caller that has no allocator of its
+ * own: a cudaMalloc on the request path would also synchronise the device.
+ * This entry point takes no workspace: the exchange scratch of the small-batch
+ * kernel lives in a fixed array inside the library's device image
+ * (DLRB200_STATIC_SCRATCH_BYTES, held by every GPU that loads the library until
+ * the process exits).  It calls no allocating routine.
+ *
+ *   Arguments as dlrb200_forward, minus workspace / workspace_bytes.
+ *   Limits: M <= DLRB200_STATIC_MAX_ROWS rows per call (r up to 256); anything
+ *   larger returns DLRB200_ERR_STATIC_LIMIT and launches nothing.  Always runs
+ *   the small-batch (striped) path.
+ *   First call on a device: looks up the device address of the array (once per
+ *   device, with that device current); make that first call before any stream
+ *   capture begins.
+ *   All calls on a device share the one array: the part a call needs is cleared
+ *   on the stream at the start of the call, and two calls that overlap on the
+ *   GPU (different streams, no dependency) race - serialise them. */
+#define DLRB200_STATIC_MAX_ROWS 64
+#define DLRB200_STATIC_SCRATCH_BYTES 200704
+DLRB200_API int dlrb200_forward_static(const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r,
+                                       int L, float eps, int* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

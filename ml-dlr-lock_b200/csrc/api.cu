@@ -228,6 +228,7 @@ const char* dlrb200_strerror(int code) {
         case DLRB200_ERR_CUDA: return "CUDA runtime or driver error (see dlrb200_last_cuda_error)";
         case DLRB200_ERR_TIMEOUT_BARRIER: return "device-side wait on the per-layer exchange gave up";
         case DLRB200_ERR_TIMEOUT_COPY: return "device-side wait on a weight copy gave up";
+        case DLRB200_ERR_STATIC_LIMIT: return "request exceeds the built-in scratch of dlrb200_forward_static (at most 64 rows per call)";
     }
     return "unknown error";
 }
@@ -326,6 +327,60 @@ int dlrb200_transpose_stack(const void* src, void* dst, int L, int rows, int col
     transpose_stack_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), rows, cols);
     return cuda_ok(cudaGetLastError()) ? DLRB200_OK : DLRB200_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------
+// Forward without any caller- or library-side allocation.
+//
+// The exchange scratch of the small-batch kernel (arrival counter + three
+// accumulator slots of 64 rows x (256+4) floats) sits in this fixed array in the
+// library's device image.  Host code may not hand `g_static_scratch` to a
+// kernel: on the host that name is only a handle for the symbol, not a device
+// address.  The address is fetched with cudaGetSymbolAddress, once per device
+// and with that device current, and cached below.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[DLRB200_STATIC_SCRATCH_BYTES];
+
+namespace {
+void* g_static_ptr[64] = {};
+std::mutex g_static_mutex;
+
+// Device address of the scratch array on the current device (set-up on first use).
+int static_scratch_ptr(void** out) {
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev))) return DLRB200_ERR_CUDA;
+    if (dev < 0 || dev >= 64) return DLRB200_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&p, g_static_scratch)) || !p) return DLRB200_ERR_CUDA;
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return DLRB200_OK;
+}
+}  // namespace
+
+int dlrb200_forward_static(const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r, int L,
+                           float eps, int* status_dev, void* stream) {
+    int rc = check_shape(M, d, r, L);
+    if (rc != DLRB200_OK) return rc;
+    if (M == 0) return DLRB200_OK;
+    if (M > DLRB200_STATIC_MAX_ROWS || striped_workspace_bytes(r) > size_t(DLRB200_STATIC_SCRATCH_BYTES))
+        return DLRB200_ERR_STATIC_LIMIT;
+    if (!x || !y || !Vp || !Up || !status_dev || x == y) return DLRB200_ERR_INVALID_ARG;
+    if (!aligned(x, 16) || !aligned(y, 16) || !aligned(Vp, 16) || !aligned(Up, 16) || !aligned(status_dev, 4))
+        return DLRB200_ERR_ALIGNMENT;
+    DevInfo di;
+    rc = device_info(&di);
+    if (rc != DLRB200_OK) return rc;
+    if (di.cc_major != 10) return DLRB200_ERR_CUDA;
+    void* scratch = nullptr;
+    rc = static_scratch_ptr(&scratch);
+    if (rc != DLRB200_OK) return rc;
+    // the striped launcher clears the counter and the accumulator slots it uses on the
+    // stream before the kernel, so whatever the previous call left behind does not matter
+    return striped_forward(x, y, Vp, Up, M, d, r, L, eps, scratch, status_dev, static_cast<cudaStream_t>(stream), di);
 }
 
 }  // extern "C"
