@@ -298,8 +298,14 @@ def main():
     timed_s = ms / 1e3
     peak_tf = peaks["tf_sustained"] if timed_s > 1.0 else peaks["tf_burst"]
     achieved_tf = flops / launches_per_step / (kernel_ms * 1e-3) / 1e12
+    # DRAM traffic per launch: one ncu capture of a one-wave launch (profiles/) showed traffic equal to the
+    # algorithmic bytes; weights exceed L2, so a launch of several waves re-reads them once per wave.
+    tiles = (M + 127) // 128
+    waves = -(-tiles // max(1, plan.grid // max(1, plan.cluster))) if plan.path == 2 else plan.passes
+    traffic = waves * 4.0 * L * d * r + 4.0 * M * d
     roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
-                "frac": achieved_tf / peak_tf, "traffic": None,
+                "frac": achieved_tf / peak_tf, "traffic": traffic,
+                "traffic_note": "bytes per launch, scaled by waves from a one-wave ncu capture",
                 "peak_source": f"{peaks['source']} ({'sustained' if timed_s > 1.0 else 'burst'})",
                 "kernel": "cluster" if plan.path == 2 else "striped", "kernel_ms": kernel_ms,
                 "frac_of_nominal_2250": achieved_tf / 2250.0}
