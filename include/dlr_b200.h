@@ -63,6 +63,7 @@ extern "C" {
 /* Execution paths reported by dlrb200_query. */
 #define DLRB200_PATH_STRIPED 1 /* small batch: width-striped CTAs, weight streaming, mma.sync */
 #define DLRB200_PATH_CLUSTER 2 /* large batch: row tiles on CTA clusters, tcgen05 + tensor memory */
+#define DLRB200_PATH_CLUSTER_SMALL 3 /* small batch: one cluster per 8 rows, exchange in distributed shared memory */
 
 typedef struct dlrb200_plan {
     int path;           /* DLRB200_PATH_* */

@@ -6,6 +6,7 @@
 
 #include "cluster.h"
 #include "decode.h"
+#include "decode_cluster.h"
 
 namespace {
 
@@ -189,6 +190,25 @@ bool use_cluster_path(int M, int d, int r, int L) {
     return M > 64;
 }
 
+// Small batches: the cluster kernel (one cluster per pair of rows, exchange in
+// distributed shared memory) or the striped kernel (all SMs on every row,
+// exchange through global memory).  Measured on B200, L about 142: at d = 1024
+// the cluster kernel wins for every M <= 64 (328 us against 337..528 us), at
+// d = 2048 for 2 <= M <= 32 (428 us against 476..650 us), at d = 4096 never
+// (a cluster of 16 SMs cannot pull 2 MB of weights per layer fast enough:
+// 666 us against 420 us at M = 1).  All its clusters must be resident at once
+// to share the weight stream through L2, hence the cap on the grid.
+// DLRB200_FORCE_PATH=1 or 3 overrides the choice.
+bool use_cluster_small(int M, int d, int r) {
+    const int forced = env_int("DLRB200_FORCE_PATH", 0);
+    if (forced == DLRB200_PATH_STRIPED || forced == DLRB200_PATH_CLUSTER) return false;
+    if (M > 64 || !dlr::decode_cluster_supported(d, r)) return false;
+    if (forced == DLRB200_PATH_CLUSTER_SMALL) return true;
+    const int grid = ((M + 1) / 2) * (d / 256);
+    if (grid > 128) return false;
+    return d <= 1024 || (d <= 2048 && M >= 2);
+}
+
 }  // namespace
 
 namespace dlr {
@@ -253,6 +273,7 @@ int dlrb200_query(int M, int d, int r, int L, dlrb200_plan* plan) {
     std::memset(plan, 0, sizeof(*plan));
     plan->workspace_bytes = dlrb200_workspace_bytes(M, d, r, L);
     if (use_cluster_path(M, d, r, L)) return dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
+    if (use_cluster_small(M, d, r)) return dlr::decode_cluster_plan(M, d, r, L, di.smem_optin, plan);
     const int dc = pick_stripe_cols(d, di.num_sms);
     if (dc == 0) return DLRB200_ERR_UNSUPPORTED_SHAPE;
     plan->path = DLRB200_PATH_STRIPED;
@@ -284,6 +305,17 @@ int dlrb200_forward(const void* x, void* y, const void* Vp, const void* Up, int 
         if (!enc) return DLRB200_ERR_CUDA;
         rc = dlr::cluster_forward(reinterpret_cast<void*>(enc), x, y, Vp, Up, M, d, r, L, eps, workspace, status_dev,
                                   st, di.num_sms, di.smem_optin, spin_limit());
+        if (rc == DLRB200_ERR_CUDA) g_last_cuda_error = int(cudaGetLastError());
+        return rc;
+    }
+    if (use_cluster_small(M, d, r)) {
+        EncodeTiledFn enc = encode_fn();
+        if (!enc) return DLRB200_ERR_CUDA;
+        rc = dlr::decode_cluster_forward(reinterpret_cast<void*>(enc), x, y, Vp, Up, M, d, r, L, eps, status_dev, st,
+                                         di.smem_optin, spin_limit(),
+                                         env_int("DLRB200_PROFILE", 0) ? reinterpret_cast<unsigned long long*>(
+                                                                             static_cast<uint8_t*>(workspace) + 256)
+                                                                       : nullptr);
         if (rc == DLRB200_ERR_CUDA) g_last_cuda_error = int(cudaGetLastError());
         return rc;
     }

@@ -247,12 +247,13 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
         // =============================== TMA producer ===============================
         if (lane == 0) {
             uint32_t n = 0;
+            RingPos rp;
             long long pw = 0;
             for (int tile = cluster_id; tile < p.num_tiles && !err; tile += num_clusters) {
                 for (int l = 0; l < p.L && !err; ++l) {
-                    for (int i = 0; i < C::LOADS_PER_LAYER; ++i, ++n) {
-                        const uint32_t st = n % uint32_t(S);
-                        const uint32_t ph = (n / uint32_t(S)) & 1u;
+                    for (int i = 0; i < C::LOADS_PER_LAYER; ++i, ++n, rp.step(uint32_t(S))) {
+                        const uint32_t st = rp.st;
+                        const uint32_t ph = rp.ph;
                         const long long t0 = DLR_CLK();
                         if (!w.cta(smem_u32(&bars->ring_empty[st]), ph ^ 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; err_layer = l; break; }
                         pw += DLR_CLK() - t0;
@@ -289,12 +290,12 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
             const uint32_t acc = tmem_base + kAcc0 + uint32_t(b) * 128u;
             const uint32_t idesc_v = umma_idesc_bf16(128, R);
             const uint32_t idesc_u = umma_idesc_bf16(128, 128);
-            uint32_t nb = 0;                     // ring position of this layer's first weight tile
+            RingPos rb;                          // ring position of this layer's first weight tile
             uint32_t c_h = 0, c_s = 0, c_e = 0;
             long long m[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             const long long mstart = DLR_CLK();
             for (int tile = cluster_id; tile < p.num_tiles && !err; tile += num_clusters) {
-                for (int l = 0; l < p.L && !err; ++l, nb += C::LOADS_PER_LAYER) {
+                for (int l = 0; l < p.L && !err; ++l, rb.advance(uint32_t(C::LOADS_PER_LAYER), uint32_t(S))) {
                     err_layer = l;
                     long long t0 = DLR_CLK();
                     if (!w.cta(smem_u32(&bars->h_ready), c_h & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
@@ -305,10 +306,10 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                     // ---- this warp's half of the V contraction
                     for (int kk = 0; kk < kKT / 2 && !err; ++kk) {
                         const int kt = b * (kKT / 2) + kk;
-                        const uint32_t idx = nb + uint32_t(kt);
-                        const uint32_t st = idx % uint32_t(S);
+                        const RingPos rq = rb.at(uint32_t(kt), uint32_t(S));
+                        const uint32_t st = rq.st;
                         const long long r0 = DLR_CLK();
-                        if (!w.cta(smem_u32(&bars->ring_full[st]), (idx / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                        if (!w.cta(smem_u32(&bars->ring_full[st]), rq.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
                         m[4] += DLR_CLK() - r0;
                         tc_fence_after();
                         const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, 2u, 1024u);
@@ -336,10 +337,10 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                         tc_fence_after();
                         m[6] += DLR_CLK() - a0;
                         for (int kh = 0; kh < C::UK && !err; ++kh) {
-                            const uint32_t idx = nb + uint32_t(kKT + nc * C::UK + kh);
-                            const uint32_t st = idx % uint32_t(S);
+                            const RingPos rq = rb.at(uint32_t(kKT + nc * C::UK + kh), uint32_t(S));
+                            const uint32_t st = rq.st;
                             const long long r0 = DLR_CLK();
-                            if (!w.cta(smem_u32(&bars->ring_full[st]), (idx / uint32_t(S)) & 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                            if (!w.cta(smem_u32(&bars->ring_full[st]), rq.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
                             m[5] += DLR_CLK() - r0;
                             tc_fence_after();
                             const uint64_t bdesc = umma_desc(ring_s + st * kStageBytes, C::U_LAYOUT, C::U_SBO);
@@ -642,8 +643,10 @@ int launch_cluster(void* enc, const void* x, void* y, const void* Vp, const void
     p.num_tiles = num_tiles;
     p.prof = prof;
     CUtensorMap tmV, tmU;
-    if (!encode_2d_bf16(enc, &tmV, Vp, uint64_t(d), uint64_t(L) * R, 64, R, 128) ||
-        !encode_2d_bf16(enc, &tmU, Up, uint64_t(R), uint64_t(L) * d, C::KW, 128, C::KW * 2))
+    memset(&tmV, 0, sizeof(tmV));
+    memset(&tmU, 0, sizeof(tmU));
+    if ((!encode_2d_bf16(enc, &tmV, Vp, uint64_t(d), uint64_t(L) * R, 64, R, 128) ||
+        !encode_2d_bf16(enc, &tmU, Up, uint64_t(R), uint64_t(L) * d, C::KW, 128, C::KW * 2)))
         return DLRB200_ERR_CUDA;
     const cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, tmV, tmU, p);
     return ce == cudaSuccess ? DLRB200_OK : DLRB200_ERR_CUDA;

@@ -102,8 +102,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
     }
     __syncthreads();
 
-    auto issue_layer = [&](int layer) {
-        const int st = layer % S;
+    auto issue_layer = [&](int layer, int st) {   // st == layer % S, kept by stepping (no division in the loop)
         const uint32_t bar = smem_u32(&full[st]);
         const uint32_t dst = ring_s + uint32_t(st) * C::STAGE_BYTES;
         mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
@@ -115,7 +114,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
 
     if (tid == 0) {
         const int pre = S < p.L ? S : p.L;
-        for (int l = 0; l < pre; ++l) issue_layer(l);
+        for (int l = 0; l < pre; ++l) issue_layer(l, l);
     }
 
     // ---- load the input stripe: h (fp32), its bf16 copy, partial sum of squares
@@ -148,10 +147,11 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
 
     int err = 0;
     int l = 0;
+    RingPos rpos;
 #pragma unroll 1
-    for (; l < p.L; ++l) {
-        const int st = l % S;
-        const uint32_t ph = (l / S) & 1;
+    for (; l < p.L; ++l, rpos.step(uint32_t(S))) {
+        const int st = int(rpos.st);
+        const uint32_t ph = rpos.ph;
         const int slot = l % 3;
         float* zs = zacc + size_t(slot) * C::MP * C::RP;
         const uint32_t vbase = ring_s + uint32_t(st) * C::STAGE_BYTES;
@@ -265,7 +265,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
         }
         __syncthreads();  // (E) stage fully consumed, dh partials visible
 
-        if (tid == 0 && l + S < p.L) issue_layer(l + S);
+        if (tid == 0 && l + S < p.L) issue_layer(l + S, st);
 
         // ---- h += dh ; partial sum of squares and bf16 copy for the next layer
         float* znext = zacc + size_t((l + 1) % 3) * C::MP * C::RP;

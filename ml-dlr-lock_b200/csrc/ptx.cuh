@@ -104,6 +104,26 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     return false;
 }
 
+// Position in a ring of `S` stages (S known only at run time): stage index and
+// phase parity, moved by stepping.  Never divide by S in a kernel loop: an
+// integer division by a run-time value is a dependent chain of a few hundred
+// cycles, and in a one-thread producer or MMA loop nothing hides it.
+struct RingPos {
+    uint32_t st = 0, ph = 0;
+    __device__ __forceinline__ void step(uint32_t S) {
+        if (++st == S) { st = 0; ph ^= 1u; }
+    }
+    __device__ __forceinline__ void advance(uint32_t k, uint32_t S) {
+        st += k;
+        while (st >= S) { st -= S; ph ^= 1u; }
+    }
+    __device__ __forceinline__ RingPos at(uint32_t k, uint32_t S) const {
+        RingPos r = *this;
+        r.advance(k, S);
+        return r;
+    }
+};
+
 // ---------------------------------------------------------------------------
 // proxy fences
 // ---------------------------------------------------------------------------
