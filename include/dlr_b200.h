@@ -63,7 +63,8 @@ extern "C" {
 /* Execution paths reported by dlrb200_query. */
 #define DLRB200_PATH_STRIPED 1 /* small batch: width-striped CTAs, weight streaming, mma.sync */
 #define DLRB200_PATH_CLUSTER 2 /* large batch: row tiles on CTA clusters, tcgen05 + tensor memory */
-#define DLRB200_PATH_CLUSTER_SMALL 3 /* small batch: one cluster per 8 rows, exchange in distributed shared memory */
+#define DLRB200_PATH_CLUSTER_SMALL 3 /* small batch: one cluster per 2 rows, exchange in distributed shared memory */
+#define DLRB200_PATH_STREAMED 4 /* large batch: one CTA per 128-row tile, activations streamed through shared memory */
 
 typedef struct dlrb200_plan {
     int path;           /* DLRB200_PATH_* */
@@ -71,7 +72,7 @@ typedef struct dlrb200_plan {
     int cluster;        /* CTAs per cluster (1 = none) */
     int stripe_cols;    /* columns of the model width owned by one CTA */
     int rows_per_pass;  /* token rows handled by one launch (striped) or one cluster tile */
-    int passes;         /* launches per forward */
+    int passes;         /* striped path: launches per forward; cluster and streamed paths: waves of row tiles in the one launch */
     int stages;         /* depth of the weight ring, in layers (striped) or tiles (cluster) */
     size_t smem_bytes;  /* dynamic shared memory per CTA */
     size_t workspace_bytes;

@@ -7,6 +7,7 @@
 #include "cluster.h"
 #include "decode.h"
 #include "decode_cluster.h"
+#include "stream.h"
 
 namespace {
 
@@ -182,9 +183,35 @@ int check_shape(int M, int d, int r, int L) {
 
 // Which path serves M rows.  The cluster path handles any M in 128-row tiles
 // once a tile's worth of rows makes the tensor-memory path pay off.
+// Large batches: the cluster kernel (activations resident in tensor memory, one
+// exchange per layer inside a cluster) or the streamed kernel (one CTA per
+// 128-row tile, no exchange, activations streamed through L2).  The cluster
+// kernel finishes a wave of tiles sooner but holds only one tile per cluster
+// (15 clusters of 8 on a B200 at d = 4096); the streamed kernel takes one tile
+// per SM.  Measured at d = 4096, r = 128, L = 143: 8192 rows 5.98 ms against
+// 6.73 ms, 9728 rows 7.15 against 6.73, 16384 rows 10.75 against 8.26, 19200 rows
+// 11.9 against 15.6 (two streamed waves).  A streamed wave costs about
+// 0.75 * (cluster size) cluster waves, at every width measured (1024, 2048, 4096).
+// Shapes the cluster kernel does not cover (d > 4096, d not a multiple of 512)
+// always stream: 3.7 ms against 27.6 ms on the striped kernel at d = 8192, M = 4096.
+bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
+    const int forced = env_int("DLRB200_FORCE_PATH", 0);
+    if (M <= 64 || !dlr::stream_supported(d, r)) return false;
+    if (forced == DLRB200_PATH_STREAMED) return true;
+    if (forced != 0) return false;
+    if (!dlr::cluster_supported(d, r, L)) return true;
+    dlrb200_plan pc, ps;
+    std::memset(&pc, 0, sizeof(pc));
+    std::memset(&ps, 0, sizeof(ps));
+    if (dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, &pc) != DLRB200_OK) return true;
+    if (dlr::stream_plan(M, d, r, L, di.num_sms, di.smem_optin, &ps) != DLRB200_OK) return false;
+    // (not calibrated for a cluster of one CTA, which has no exchange to lose time in)
+    return pc.cluster >= 2 && pc.passes >= 2 && 4 * pc.passes >= 3 * pc.cluster * ps.passes;
+}
+
 bool use_cluster_path(int M, int d, int r, int L) {
     const int forced = env_int("DLRB200_FORCE_PATH", 0);
-    if (forced == DLRB200_PATH_STRIPED) return false;
+    if (forced == DLRB200_PATH_STRIPED || forced == DLRB200_PATH_STREAMED || forced == DLRB200_PATH_CLUSTER_SMALL) return false;
     if (!dlr::cluster_supported(d, r, L)) return false;
     if (forced == DLRB200_PATH_CLUSTER) return true;
     return M > 64;
@@ -272,6 +299,7 @@ int dlrb200_query(int M, int d, int r, int L, dlrb200_plan* plan) {
     if (rc != DLRB200_OK) return rc;
     std::memset(plan, 0, sizeof(*plan));
     plan->workspace_bytes = dlrb200_workspace_bytes(M, d, r, L);
+    if (use_stream_path(M, d, r, L, di)) return dlr::stream_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
     if (use_cluster_path(M, d, r, L)) return dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
     if (use_cluster_small(M, d, r)) return dlr::decode_cluster_plan(M, d, r, L, di.smem_optin, plan);
     const int dc = pick_stripe_cols(d, di.num_sms);
@@ -300,6 +328,17 @@ int dlrb200_forward(const void* x, void* y, const void* Vp, const void* Up, int 
     if (rc != DLRB200_OK) return rc;
     if (di.cc_major != 10) return DLRB200_ERR_CUDA;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (use_stream_path(M, d, r, L, di) && dlr::stream_aligned(x, y)) {
+        EncodeTiledFn enc = encode_fn();
+        if (!enc) return DLRB200_ERR_CUDA;
+        rc = dlr::stream_forward(reinterpret_cast<void*>(enc), x, y, Vp, Up, M, d, r, L, eps, status_dev, st, di.num_sms,
+                                 di.smem_optin, spin_limit(),
+                                 env_int("DLRB200_PROFILE", 0) ? reinterpret_cast<unsigned long long*>(
+                                                                     static_cast<uint8_t*>(workspace) + 256)
+                                                               : nullptr);
+        if (rc == DLRB200_ERR_CUDA) g_last_cuda_error = int(cudaGetLastError());
+        return rc;
+    }
     if (use_cluster_path(M, d, r, L)) {
         EncodeTiledFn enc = encode_fn();
         if (!enc) return DLRB200_ERR_CUDA;

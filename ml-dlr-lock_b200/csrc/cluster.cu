@@ -94,84 +94,7 @@ struct CCfg {
     static constexpr int FIXED_BYTES = S_BYTES + RECV_BYTES + 1024 /*barriers*/ + 1024 /*alignment*/;
 };
 
-// K-major shared-memory operand descriptor: 8-row groups `sbo` bytes apart,
-// swizzle span 128 B (layout 2) or 64 B (layout 4); version 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t layout, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= uint64_t((saddr & 0x3ffffu) >> 4);
-    d |= uint64_t(1) << 16;
-    d |= uint64_t(sbo >> 4) << 32;
-    d |= uint64_t(1) << 46;
-    d |= uint64_t(layout) << 61;
-    return d;
-}
-
-// Shared-memory operand descriptor for the un-swizzled K-major layout: core
-// matrices of 8 rows x 16 bytes, `lbo` bytes apart along K, `sbo` bytes apart
-// along the rows.
-__device__ __forceinline__ uint64_t umma_desc_nosw(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= uint64_t((saddr & 0x3ffffu) >> 4);
-    d |= uint64_t(lbo >> 4) << 16;
-    d |= uint64_t(sbo >> 4) << 32;
-    d |= uint64_t(1) << 46;
-    return d;
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "r"(taddr)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(v[0]),
-                 "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
-                 : "memory");
-}
-
-// Asynchronous 16-byte store into a peer's (or this CTA's own) shared memory;
-// the 16 bytes are counted on the RECEIVER's mbarrier.  Both addresses are
-// shared::cluster addresses from mapa().
-__device__ __forceinline__ void st_async_v4(uint32_t dst_cluster, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
-                                            uint32_t bar_cluster) {
-    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1,%2,%3,%4}, [%5];" ::"r"(
-                     dst_cluster),
-                 "r"(a), "r"(b), "r"(c), "r"(d), "r"(bar_cluster)
-                 : "memory");
-}
-
 #define DLR_CLK() (p.prof ? clock64() : 0ll)
-
-struct Waiter {
-    volatile int* abort_flag;
-    uint32_t limit;
-    __device__ __forceinline__ bool cta(uint32_t bar, uint32_t parity) const {
-        for (uint32_t i = 0; i < limit; ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
-            if ((i & 63u) == 63u && *abort_flag) return false;
-        }
-        return false;
-    }
-    __device__ __forceinline__ bool cluster(uint32_t bar, uint32_t parity) const {
-        for (uint32_t i = 0; i < limit; ++i) {
-            if (mbar_try_wait_cluster(bar, parity)) return true;
-            if ((i & 63u) == 63u && *abort_flag) return false;
-        }
-        return false;
-    }
-};
 
 struct Bars {
     uint64_t ring_full[kMaxStages];
@@ -277,7 +200,7 @@ dlr_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constan
                 // wait (bounded) for them before leaving.
                 for (uint32_t back = 1; back <= uint32_t(S) && back <= n; ++back) {
                     const uint32_t m = n - back;
-                    mbar_wait(smem_u32(&bars->ring_full[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, p.spin_limit >> 6);
+                    mbar_wait(smem_u32(&bars->ring_full[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, kDrainPolls);
                 }
             }
         }
@@ -627,7 +550,7 @@ int launch_cluster(void* enc, const void* x, void* y, const void* Vp, const void
         plan_only->cluster = CS;
         plan_only->stripe_cols = kStripe;
         plan_only->rows_per_pass = kRows;
-        plan_only->passes = 1;
+        plan_only->passes = (num_tiles + clusters - 1) / clusters;   // waves of row tiles
         plan_only->stages = stages;
         plan_only->smem_bytes = size_t(smem);
         return DLRB200_OK;

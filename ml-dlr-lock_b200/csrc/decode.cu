@@ -305,7 +305,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
             atomicCAS(p.status, 0, err | (l << 8));
             const int hi = (l + S < p.L) ? l + S : p.L;
             const int lo = (err == DLRB200_ERR_TIMEOUT_COPY) ? l : l + 1;
-            for (int j = lo; j < hi; ++j) mbar_wait(smem_u32(&full[j % S]), (j / S) & 1, p.spin_limit >> 4);
+            for (int j = lo; j < hi; ++j) mbar_wait(smem_u32(&full[j % S]), (j / S) & 1, kDrainPolls);
         }
         __syncthreads();
     }

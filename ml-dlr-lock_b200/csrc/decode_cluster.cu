@@ -220,7 +220,7 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
                 // tiles already requested still land in this CTA's ring: wait (bounded) before leaving
                 for (uint32_t back = 1; back <= uint32_t(S) && back <= n; ++back) {
                     const uint32_t m = n - back;   // error path only: the division does not matter here
-                    mbar_wait(smem_u32(&bars->full[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, p.spin_limit >> 6);
+                    mbar_wait(smem_u32(&bars->full[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, kDrainPolls);
                 }
             }
         }

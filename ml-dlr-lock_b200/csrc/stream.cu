@@ -1,0 +1,618 @@
+// Large-batch ("prefill") DLR-Net forward, streamed path: one CTA walks one
+// 128-row tile of the batch through all L layers and the whole width d.  The
+// activations stream through registers and tensor memory chunk by chunk, in
+// place in the output buffer; shared memory holds nothing but weights, and no
+// CTA ever waits for another.
+//
+// Why.  Rows are independent (dlr_lock/model.py:96-100 acts on each token
+// alone), so a CTA that owns whole rows needs no exchange.  A tile of 128 rows
+// x d does not fit on chip, but it does not have to: the update of a layer is
+// h[:, c] += s * U'[c, :]^T column chunk by column chunk, and the next layer's
+// contraction z = h * V'^T can take a chunk as soon as it is updated.  The two
+// contractions of neighbouring layers therefore run interleaved on the tensor
+// core, and the only serial point per layer is the normalise + SiLU step.
+//
+// What bounds it.  With 128 rows per SM every weight byte is written to shared
+// memory once (TMA) and read from it once (the MMA's B operand); at the tensor
+// core's rate that alone is the whole 128 B/clk of the shared-memory port.  So
+// as little else as possible goes through shared memory: both A operands (s
+// and the updated chunk) are bf16 in tensor memory (tcgen05.mma with A in
+// TMEM); the old values of a chunk come in by TMA (a thread owns a row, so
+// plain loads would touch 32 cache lines per instruction) and the new values
+// go straight from registers to global memory (L2 at these batch sizes), 32
+// bytes at a time.
+//
+// Per chunk c of layer l (steady state), 128 rows x 128 columns, on one of two
+// tensor-memory buffers of 128 columns:
+//   producer warp   TMA loads of the old chunk, of U'[l] rows of the chunk and
+//                   of V'[l+1] columns of the chunk into three rings
+//   U-MMA warp      dh = s(l) * U'[l][chunk]^T  -> buffer (fp32)
+//   epilogue warps  h_new = h_old + dh (fp32 add, rounded once to bf16): h_old
+//                   from shared memory, h_new to global memory and, packed
+//                   bf16, back into the buffer over the dh it came from;
+//                   running sum of squares per row
+//   V-MMA warp      z(l+1) += h_new[chunk] * V'[l+1][:, chunk]^T  (A = buffer)
+// After the last chunk z(l+1) is complete; the epilogue warps turn it into
+// s(l+1) = silu(z * rsqrt(sumsq / d + eps)), bf16, into tensor memory.
+//
+// Layer 0 is preceded by a pass that only feeds x to the V-MMA warp.  Passes
+// 0 and -1 read x, every pass >= 0 writes y and every pass >= 1 reads y, so x
+// is never modified.  A chunk written in one pass is read by TMA in the next:
+// the writers fence towards the async proxy before they release the staging
+// slot, and the producer acquires a later release of a slot before it asks
+// for the chunk.
+//
+// All waits are bounded; a wait that gives up raises an abort flag, records a
+// status word and every role drains and leaves.
+#include <cstring>
+
+#include "ptx.cuh"
+#include "stream.h"
+
+namespace dlr {
+
+namespace {
+
+constexpr int kRowsS = 128;              // rows per tile
+constexpr int kCW = 128;                 // columns per chunk
+constexpr int kThreadsS = 384;           // 12 warps: producer, U-MMA, V-MMA, (tensor-memory owner), 8 epilogue
+constexpr int kEpiWarps = 8;
+constexpr int kMaxW = 8;                 // most stages of a weight ring
+constexpr int kNH = 2;                   // old chunks in flight
+constexpr int kHBytes = 2 * 16384;       // one chunk: two tiles of 128 rows x 64 columns (128-byte swizzle)
+constexpr uint32_t kZCol = 0;            // tensor-memory columns: z accumulator (R columns)
+constexpr uint32_t kSCol = 128;          //   s, bf16 packed two per column (R/2 columns)
+constexpr uint32_t kACol = 192;          //   the updated chunk, bf16 packed two per column (64 columns)
+constexpr uint32_t kBufCol = 256;        //   two dh accumulators of 128 columns
+
+template <int R>
+struct SCfg {
+    static constexpr int UT = R / 64;                    // U' tiles per chunk: 128 rows x 64 K-columns
+    static constexpr int U_BYTES = UT * 16384;
+    static constexpr int V_TILE_BYTES = R * 128;         // V' tile: R rows x 64 K-columns
+    static constexpr int V_BYTES = 2 * V_TILE_BYTES;
+    static constexpr int NU = R == 128 ? 2 : 4;          // stages of the U' ring
+    static constexpr int NV = R == 128 ? 3 : 6;          // stages of the V' ring (held until the chunk is updated)
+    static constexpr int SMEM_BYTES = kNH * kHBytes + NU * U_BYTES + NV * V_BYTES + 1024 /*sums of squares*/ + 512 /*barriers*/ +
+                                      1024 /*alignment*/;
+};
+
+struct SBars {
+    uint64_t u_full[kMaxW], u_empty[kMaxW];
+    uint64_t v_full[kMaxW], v_empty[kMaxW];
+    uint64_t h_full[kNH];     // old chunk has landed (TMA bytes)
+    uint64_t h_empty[kNH];    // the 8 epilogue warps have read it
+    uint64_t dh_full[2];      // U-MMA warp: dh of the chunk is in the buffer
+    uint64_t dh_empty[2];     // 8 epilogue warps: dh has been read
+    uint64_t a_ready;         // 8 epilogue warps: the updated chunk (bf16) is in tensor memory
+    uint64_t a_empty;         // V-MMA warp: the chunk has been read
+    uint64_t z_full, s_ready;
+    uint64_t ssq_bar;         // the 8 epilogue warps have published their halves of the sums of squares
+    uint64_t drain[2];        // all tensor-core work of an MMA warp is complete (waited for before leaving)
+    uint32_t tmem_slot;
+    int abort_flag;
+};
+static_assert(sizeof(SBars) <= 512, "barrier block");
+
+struct SParams {
+    const __nv_bfloat16* x;
+    __nv_bfloat16* y;
+    int M, d, L;
+    int nch;                  // chunks per row: d / 128
+    int num_tiles;
+    float eps, inv_d;
+    int* status;
+    unsigned int spin_limit;
+    unsigned long long* prof; // optional cycle counters (debug), or null
+};
+
+#define DLS_CLK() (p.prof ? clock64() : 0ll)
+
+// 32-byte global accesses: a thread owns 128 contiguous bytes of its row per chunk, so these move whole sectors.
+__device__ __forceinline__ void ldg32(const void* ptr, uint32_t (&v)[8]) {
+    asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "l"(ptr)
+                 : "memory");
+}
+__device__ __forceinline__ void stg32(void* ptr, const uint32_t (&v)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+
+// Non-blocking test of an mbarrier phase (try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+template <int R>
+__global__ void __launch_bounds__(kThreadsS, 1)
+dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmU, SParams p) {
+    using C = SCfg<R>;
+    constexpr uint32_t NU = C::NU, NV = C::NV;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* hbuf = smem;
+    uint8_t* ubuf = hbuf + kNH * kHBytes;
+    uint8_t* vbuf = ubuf + NU * C::U_BYTES;
+    float* ssqx = reinterpret_cast<float*>(vbuf + NV * C::V_BYTES);   // [2 halves][128 rows]
+    SBars* bars = reinterpret_cast<SBars*>(ssqx + 2 * kRowsS);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const Waiter w{abort_flag, p.spin_limit >> 2};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMaxW; ++s) {
+            mbar_init(smem_u32(&bars->u_full[s]), 1);
+            mbar_init(smem_u32(&bars->u_empty[s]), 1);
+            mbar_init(smem_u32(&bars->v_full[s]), 1);
+            mbar_init(smem_u32(&bars->v_empty[s]), 1);
+        }
+        for (int s = 0; s < kNH; ++s) {
+            mbar_init(smem_u32(&bars->h_full[s]), 1);
+            mbar_init(smem_u32(&bars->h_empty[s]), kEpiWarps);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars->dh_full[b]), 1);
+            mbar_init(smem_u32(&bars->dh_empty[b]), kEpiWarps);
+        }
+        mbar_init(smem_u32(&bars->a_ready), kEpiWarps);
+        mbar_init(smem_u32(&bars->a_empty), 1);
+        mbar_init(smem_u32(&bars->z_full), 1);
+        mbar_init(smem_u32(&bars->s_ready), kEpiWarps);
+        mbar_init(smem_u32(&bars->ssq_bar), kEpiWarps);
+        mbar_init(smem_u32(&bars->drain[0]), 1);
+        mbar_init(smem_u32(&bars->drain[1]), 1);
+        bars->abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmX);
+        tma_prefetch_desc(&tmY);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmU);
+    }
+    if (warp == 3) {
+        tmem_alloc(smem_u32(&bars->tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_slot;
+    const uint32_t hbuf_s = smem_u32(hbuf), ubuf_s = smem_u32(ubuf), vbuf_s = smem_u32(vbuf);
+    const int nch = p.nch;
+    const int my_tiles = (p.num_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+
+    int err = 0;
+    int err_layer = 0;
+
+    // A pass q = -1 .. L-1 walks the nch chunks once.  Pass q >= 0 applies the update of layer q; pass q < L-1
+    // feeds the V contraction of layer q+1.  Chunk number n (all tiles, all passes) uses buffer n & 1.
+    if (warp == 0) {
+        // =============================== TMA producer ===============================
+        // The two rings advance independently: whichever has a free stage gets its next tile.
+        if (lane == 0) {
+            RingPos up, vp, hp;
+            int uph[kMaxW], vph[kMaxW], hph[kNH];   // parity of the last copy requested into each stage, -1: none
+            for (int i = 0; i < kMaxW; ++i) uph[i] = vph[i] = -1;
+            for (int i = 0; i < kNH; ++i) hph[i] = -1;
+            const long long total = (long long)my_tiles * p.L * nch;          // tiles of each weight stream
+            const long long total_h = (long long)my_tiles * (p.L + 1) * nch;  // chunks of activations
+            long long nu = 0, nv = 0, nh = 0;
+            int uq = 0, uc = 0, vq = 0, vc = 0;
+            int ht = 0, hq = -1, hc = 0;
+            uint32_t idle = 0;
+            while ((nu < total || nv < total || nh < total_h) && !err) {
+                bool did = false;
+                if (nh < total_h && mbar_test_wait(smem_u32(&bars->h_empty[hp.st]), hp.ph ^ 1u)) {
+                    // pass >= 1 reads what this CTA's epilogue threads stored one pass earlier; they fenced those
+                    // stores towards the async proxy before the release of a staging slot observed above
+                    const uint32_t bar = smem_u32(&bars->h_full[hp.st]);
+                    const uint32_t dst = hbuf_s + hp.st * kHBytes;
+                    const CUtensorMap* src = hq >= 1 ? &tmY : &tmX;
+                    const int m0 = (int(blockIdx.x) + ht * int(gridDim.x)) * kRowsS;
+                    mbar_arrive_expect_tx(bar, kHBytes);
+                    tma_load_2d(dst, src, hc * kCW, m0, bar);
+                    tma_load_2d(dst + 16384, src, hc * kCW + 64, m0, bar);
+                    hph[hp.st] = int(hp.ph);
+                    hp.step(kNH);
+                    ++nh;
+                    if (++hc == nch) { hc = 0; if (++hq == p.L) { hq = -1; ++ht; } }
+                    did = true;
+                }
+                if (nu < total && mbar_test_wait(smem_u32(&bars->u_empty[up.st]), up.ph ^ 1u)) {
+                    const uint32_t bar = smem_u32(&bars->u_full[up.st]);
+                    const uint32_t dst = ubuf_s + up.st * C::U_BYTES;
+                    mbar_arrive_expect_tx(bar, C::U_BYTES);
+#pragma unroll
+                    for (int t = 0; t < C::UT; ++t) tma_load_2d(dst + t * 16384, &tmU, 64 * t, uq * p.d + uc * kCW, bar);
+                    uph[up.st] = int(up.ph);
+                    up.step(NU);
+                    ++nu;
+                    if (++uc == nch) { uc = 0; if (++uq == p.L) uq = 0; }
+                    did = true;
+                }
+                if (nv < total && mbar_test_wait(smem_u32(&bars->v_empty[vp.st]), vp.ph ^ 1u)) {
+                    const uint32_t bar = smem_u32(&bars->v_full[vp.st]);
+                    const uint32_t dst = vbuf_s + vp.st * C::V_BYTES;
+                    mbar_arrive_expect_tx(bar, C::V_BYTES);
+                    tma_load_2d(dst, &tmV, vc * kCW, vq * R, bar);
+                    tma_load_2d(dst + C::V_TILE_BYTES, &tmV, vc * kCW + 64, vq * R, bar);
+                    vph[vp.st] = int(vp.ph);
+                    vp.step(NV);
+                    ++nv;
+                    if (++vc == nch) { vc = 0; if (++vq == p.L) vq = 0; }
+                    did = true;
+                }
+                if (did) {
+                    idle = 0;
+                } else if (++idle > p.spin_limit || ((idle & 63u) == 63u && *abort_flag)) {
+                    err = DLRB200_ERR_TIMEOUT_COPY;
+                    err_layer = uq;
+                }
+            }
+            if (err || *abort_flag) {
+                // copies requested before giving up still land in this CTA's shared memory: wait for them
+                for (int i = 0; i < kNH; ++i)
+                    if (hph[i] >= 0) mbar_wait(smem_u32(&bars->h_full[i]), uint32_t(hph[i]), kDrainPolls);
+                for (int i = 0; i < int(NU); ++i)
+                    if (uph[i] >= 0) mbar_wait(smem_u32(&bars->u_full[i]), uint32_t(uph[i]), kDrainPolls);
+                for (int i = 0; i < int(NV); ++i)
+                    if (vph[i] >= 0) mbar_wait(smem_u32(&bars->v_full[i]), uint32_t(vph[i]), kDrainPolls);
+            }
+        }
+    } else if (warp == 1) {
+        // =============================== U-MMA warp ================================
+        // buffer = s(q)[128 x R] * U'[q][chunk rows, :]^T, A from tensor memory
+        if (lane == 0) {
+            constexpr uint32_t idesc_u = umma_idesc_bf16(128, kCW);
+            RingPos up;
+            uint32_t n = 0;
+            uint32_t c_s = 0;
+            long long mw[3] = {0, 0, 0};
+            for (int t = 0; t < my_tiles && !err; ++t) {
+                for (int q = 0; q < p.L && !err; ++q) {
+                    err_layer = q;
+                    long long t0 = DLS_CLK();
+                    if (!w.cta(smem_u32(&bars->s_ready), c_s & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    ++c_s;
+                    tc_fence_after();
+                    mw[0] += DLS_CLK() - t0;
+                    for (int c = 0; c < nch; ++c, ++n) {
+                        const uint32_t b = n & 1u;
+                        t0 = DLS_CLK();
+                        if (!w.cta(smem_u32(&bars->u_full[up.st]), up.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                        const long long t1 = DLS_CLK();
+                        mw[1] += t1 - t0;
+                        if (!w.cta(smem_u32(&bars->dh_empty[b]), ((n >> 1) & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        mw[2] += DLS_CLK() - t1;
+                        tc_fence_after();
+                        const uint32_t acc = tmem_base + kBufCol + b * 128u;
+                        const uint32_t ub = ubuf_s + up.st * C::U_BYTES;
+#pragma unroll
+                        for (int k = 0; k < R / 16; ++k) {
+                            const uint64_t bdesc = umma_desc(ub + uint32_t(k / 4) * 16384u, 2u, 1024u) + uint64_t(2 * (k % 4));
+                            umma_ts(acc, tmem_base + kSCol + uint32_t(8 * k), bdesc, idesc_u, k ? 1u : 0u);
+                        }
+                        umma_commit(smem_u32(&bars->u_empty[up.st]));
+                        umma_commit(smem_u32(&bars->dh_full[b]));
+                        up.step(NU);
+                    }
+                }
+            }
+            umma_commit(smem_u32(&bars->drain[0]));
+            mbar_wait(smem_u32(&bars->drain[0]), 0, kDrainPolls);
+            if (p.prof) for (int k = 0; k < 3; ++k) p.prof[blockIdx.x * 32 + 4 + k] = (unsigned long long)mw[k];
+        }
+    } else if (warp == 2) {
+        // =============================== V-MMA warp ================================
+        // z(q+1)[128 x R] += h_new[chunk][128 x 128] * V'[q+1][:, chunk]^T, A = the updated chunk in tensor memory
+        if (lane == 0) {
+            constexpr uint32_t idesc_v = umma_idesc_bf16(128, R);
+            RingPos vp;
+            uint32_t n = 0;
+            long long mw[2] = {0, 0};
+            for (int t = 0; t < my_tiles && !err; ++t) {
+                for (int q = -1; q < p.L && !err; ++q) {
+                    err_layer = q;
+                    const bool feeds = q + 1 < p.L;
+                    for (int c = 0; c < nch; ++c, ++n) {
+                        long long t0 = DLS_CLK();
+                        if (!w.cta(smem_u32(&bars->a_ready), n & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        mw[0] += DLS_CLK() - t0;
+                        if (feeds) {
+                            t0 = DLS_CLK();
+                            if (!w.cta(smem_u32(&bars->v_full[vp.st]), vp.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                            mw[1] += DLS_CLK() - t0;
+                            tc_fence_after();
+                            const uint32_t a0 = tmem_base + kACol;
+                            const uint32_t vb = vbuf_s + vp.st * C::V_BYTES;
+#pragma unroll
+                            for (int k = 0; k < kCW / 16; ++k) {
+                                const uint64_t bdesc = umma_desc(vb + uint32_t(k / 4) * C::V_TILE_BYTES, 2u, 1024u) + uint64_t(2 * (k % 4));
+                                umma_ts(tmem_base + kZCol, a0 + uint32_t(8 * k), bdesc, idesc_v, (c | k) ? 1u : 0u);
+                            }
+                            umma_commit(smem_u32(&bars->v_empty[vp.st]));
+                            umma_commit(smem_u32(&bars->a_empty));
+                            vp.step(NV);
+                        } else {
+                            mbar_arrive(smem_u32(&bars->a_empty));   // last layer: nothing reads the chunk here
+                        }
+                    }
+                    if (err) break;
+                    if (feeds) umma_commit(smem_u32(&bars->z_full));
+                }
+            }
+            umma_commit(smem_u32(&bars->drain[1]));
+            mbar_wait(smem_u32(&bars->drain[1]), 0, kDrainPolls);
+            if (p.prof) for (int k = 0; k < 2; ++k) p.prof[blockIdx.x * 32 + 8 + k] = (unsigned long long)mw[k];
+        }
+    } else if (warp >= 4) {
+        // =============================== epilogue warps =============================
+        // Two threads per row: thread (row er, half hh) owns 64 of the 128 columns of every chunk and half of
+        // the columns of z.  Warp w reads tensor-memory lanes 32 * (w % 4) .. + 31.
+        const int q4 = warp & 3;
+        const int hh = (warp - 4) >> 2;
+        const int er = 32 * q4 + lane;
+        const uint32_t tl = tmem_base + (uint32_t(32 * q4) << 16);
+        uint32_t n = 0;                      // chunks seen (all passes): phase of the A operand's barriers
+        uint32_t nu = 0;                     // chunks of update passes: accumulator nu & 1
+        uint32_t c_z = 0;
+        long long ew[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+
+        RingPos hp;
+        const uint32_t x7 = uint32_t(er & 7);
+        for (int t = 0; t < my_tiles && !err; ++t) {
+            float ssq = 0.f;
+            for (int q = -1; q < p.L && !err; ++q) {
+                err_layer = q;
+                for (int c = 0; c < nch; ++c, ++n) {
+                    const uint32_t b = nu & 1u;
+                    const uint32_t buf = tl + kBufCol + b * 128u + uint32_t(64 * hh);
+                    // ---- old values of the chunk: this thread's 128 bytes of its row, from the staging slot
+                    long long t0 = DLS_CLK();
+                    if (!w.cta(smem_u32(&bars->h_full[hp.st]), hp.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                    ew[4] += DLS_CLK() - t0;
+                    uint32_t cur[32];
+                    {
+                        const uint8_t* rowp = hbuf + hp.st * kHBytes + hh * 16384 + er * 128;
+#pragma unroll
+                        for (int ch = 0; ch < 8; ++ch) {
+                            const uint4 hv = *reinterpret_cast<const uint4*>(rowp + ((uint32_t(ch) ^ x7) << 4));
+                            cur[4 * ch] = hv.x; cur[4 * ch + 1] = hv.y; cur[4 * ch + 2] = hv.z; cur[4 * ch + 3] = hv.w;
+                        }
+                    }
+                    uint32_t out[32];
+                    t0 = DLS_CLK();
+                    if (q >= 0) {
+                        if (!w.cta(smem_u32(&bars->dh_full[b]), (nu >> 1) & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        ++nu;
+                        ew[1] += DLS_CLK() - t0;
+                        tc_fence_after();
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) {
+                            uint32_t dv[32];
+                            tmem_ld32(buf + uint32_t(32 * g), dv);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const uint32_t hw = cur[16 * g + j];
+                                const float f0 = bf16lo_to_f(hw) + __uint_as_float(dv[2 * j]);
+                                const float f1 = bf16hi_to_f(hw) + __uint_as_float(dv[2 * j + 1]);
+                                ssq = fmaf(f0, f0, ssq);
+                                ssq = fmaf(f1, f1, ssq);
+                                out[16 * g + j] = pack_bf16x2(f0, f1);
+                            }
+                        }
+                        // dh has been read: the U-MMA warp may overwrite the accumulator
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->dh_empty[b]));
+                        ew[0] += DLS_CLK() - t0;
+                    } else {
+                        // pass over x: the chunk goes to the tensor core as it is
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float f0 = bf16lo_to_f(cur[j]), f1 = bf16hi_to_f(cur[j]);
+                            ssq = fmaf(f0, f0, ssq);
+                            ssq = fmaf(f1, f1, ssq);
+                            out[j] = cur[j];
+                        }
+                    }
+                    // ---- the chunk (bf16) becomes the A operand of the next layer's contraction
+                    const long long t2 = DLS_CLK();
+                    if (!w.cta(smem_u32(&bars->a_empty), (n & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    ew[5] += DLS_CLK() - t2;
+                    tc_fence_after();
+                    tmem_st16(tl + kACol + uint32_t(32 * hh), *reinterpret_cast<uint32_t(*)[16]>(&out[0]));
+                    tmem_st16(tl + kACol + uint32_t(32 * hh + 16), *reinterpret_cast<uint32_t(*)[16]>(&out[16]));
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(smem_u32(&bars->h_empty[hp.st]));
+                        mbar_arrive(smem_u32(&bars->a_ready));
+                    }
+                    hp.step(kNH);
+                    ew[6] += DLS_CLK() - t2;
+                    if (q >= 0) {
+                        // ---- new values to global memory.  A thread holds 128 contiguous bytes of its own row, so a
+                        // plain store would touch 32 cache lines per instruction; the four lanes of a quad trade
+                        // sectors instead, and every store instruction then writes whole 128-byte lines (one row per
+                        // quad): in round k a lane receives sector k of row (lane ^ k), and instruction j stores, per
+                        // quad, row j of the quad, lane s storing sector s ^ j.
+                        const long long t3 = DLS_CLK();
+                        // the stores of the chunk before are long complete; the next pass reads them by TMA
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                        uint32_t rv[4][8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) rv[0][i] = out[i];
+#pragma unroll
+                        for (int k = 1; k < 4; ++k)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) rv[k][i] = __shfl_xor_sync(0xffffffffu, out[8 * k + i], k);
+                        const int sq = lane & 3;
+                        const int qrow = (int(blockIdx.x) + t * int(gridDim.x)) * kRowsS + 32 * q4 + (lane & ~3);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int tt = sq ^ j;
+                            uint32_t sv[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const uint32_t lo = (tt & 1) ? rv[1][i] : rv[0][i];
+                                const uint32_t hi = (tt & 1) ? rv[3][i] : rv[2][i];
+                                sv[i] = (tt & 2) ? hi : lo;
+                            }
+                            const int grow = qrow + j;
+                            if (grow < p.M) stg32(p.y + size_t(grow) * p.d + c * kCW + 64 * hh + 16 * tt, sv);
+                        }
+                        ew[7] += DLS_CLK() - t3;
+                    }
+                }
+                if (err) break;
+                if (q + 1 < p.L) {
+                    // ---- z(q+1) is complete after the V-MMA warp's last chunk: s = silu(z * rstd) -> tensor memory
+                    const long long t0 = DLS_CLK();
+                    ssqx[hh * kRowsS + er] = ssq;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->ssq_bar));
+                    if (!w.cta(smem_u32(&bars->ssq_bar), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    const float tot = ssq + ssqx[(hh ^ 1) * kRowsS + er];
+                    const float rstd = rsqrtf(tot * p.inv_d + p.eps);
+                    ssq = 0.f;
+                    if (!w.cta(smem_u32(&bars->z_full), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    ++c_z;
+                    ew[2] += DLS_CLK() - t0;
+                    tc_fence_after();
+                    constexpr int NZ = R / 2;            // columns of z per thread
+#pragma unroll
+                    for (int g = 0; g < NZ / 32; ++g) {
+                        uint32_t zv[32];
+                        tmem_ld32(tl + kZCol + uint32_t(hh * NZ + 32 * g), zv);
+                        tmem_wait_ld();
+                        uint32_t sv[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            sv[j] = pack_bf16x2(silu_f(__uint_as_float(zv[2 * j]) * rstd),
+                                                silu_f(__uint_as_float(zv[2 * j + 1]) * rstd));
+                        tmem_st16(tl + kSCol + uint32_t(hh * (NZ / 2) + 16 * g), sv);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->s_ready));
+                    ew[3] += DLS_CLK() - t0;
+                }
+            }
+        }
+        if (p.prof && threadIdx.x == 128)
+            for (int k = 0; k < 8; ++k) p.prof[blockIdx.x * 32 + 12 + k] = (unsigned long long)ew[k];
+    }
+
+    // ---- leave: report, let every role arrive, free tensor memory
+    if (err) {
+        if (!*abort_flag) {
+            *abort_flag = 1;
+            atomicCAS(p.status, 0, err | ((err_layer & 0xffff) << 8));
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 3) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+template <int R>
+int launch_stream(void* enc, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int L, float eps,
+                  int* status_dev, cudaStream_t stream, int num_sms, int smem_optin, unsigned int spin_limit,
+                  dlrb200_plan* plan_only, unsigned long long* prof) {
+    using C = SCfg<R>;
+    if (C::SMEM_BYTES > smem_optin) return DLRB200_ERR_OCCUPANCY;
+    const int num_tiles = (M + kRowsS - 1) / kRowsS;
+    const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+    if (plan_only) {
+        plan_only->path = DLRB200_PATH_STREAMED;
+        plan_only->grid = grid;
+        plan_only->cluster = 1;
+        plan_only->stripe_cols = kCW;
+        plan_only->rows_per_pass = kRowsS;
+        plan_only->passes = (num_tiles + grid - 1) / grid;
+        plan_only->stages = C::NU + C::NV;
+        plan_only->smem_bytes = size_t(C::SMEM_BYTES);
+        return DLRB200_OK;
+    }
+    auto kern = dlr_stream_kernel<R>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+        return DLRB200_ERR_CUDA;
+    CUtensorMap tmX, tmY, tmV, tmU;
+    if (!encode_2d_bf16(enc, &tmX, x, uint64_t(d), uint64_t(M), 64, kRowsS, 128) ||
+        !encode_2d_bf16(enc, &tmY, y, uint64_t(d), uint64_t(M), 64, kRowsS, 128) ||
+        !encode_2d_bf16(enc, &tmV, Vp, uint64_t(d), uint64_t(L) * R, 64, R, 128) ||
+        !encode_2d_bf16(enc, &tmU, Up, uint64_t(R), uint64_t(L) * d, 64, 128, 128))
+        return DLRB200_ERR_CUDA;
+    SParams p;
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.y = static_cast<__nv_bfloat16*>(y);
+    p.M = M; p.d = d; p.L = L;
+    p.nch = d / kCW;
+    p.num_tiles = num_tiles;
+    p.eps = eps;
+    p.inv_d = 1.0f / float(d);
+    p.status = status_dev;
+    p.spin_limit = spin_limit;
+    p.prof = prof;
+    kern<<<grid, kThreadsS, C::SMEM_BYTES, stream>>>(tmX, tmY, tmV, tmU, p);
+    return cudaGetLastError() == cudaSuccess ? DLRB200_OK : DLRB200_ERR_CUDA;
+}
+
+int dispatch_stream(void* enc, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r, int L,
+                    float eps, int* status_dev, cudaStream_t stream, int num_sms, int smem_optin,
+                    unsigned int spin_limit, dlrb200_plan* plan_only, unsigned long long* prof) {
+    switch (r) {
+        case 64: return launch_stream<64>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
+        case 128: return launch_stream<128>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
+    }
+    return DLRB200_ERR_UNSUPPORTED_SHAPE;
+}
+
+}  // namespace
+
+// The producer asks for a chunk up to two chunks ahead of the epilogue; a row of at least four chunks keeps
+// that well behind the stores of the pass before.
+bool stream_supported(int d, int r) { return (r == 64 || r == 128) && d % kCW == 0 && d >= 4 * kCW; }
+
+// The epilogue moves the activations 32 bytes at a time.
+bool stream_aligned(const void* x, const void* y) {
+    return (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
+}
+
+int stream_plan(int M, int d, int r, int L, int num_sms, int smem_optin, dlrb200_plan* plan) {
+    const size_t ws = plan->workspace_bytes;
+    const int rc = dispatch_stream(nullptr, nullptr, nullptr, nullptr, nullptr, M, d, r, L, 0.f, nullptr, nullptr, num_sms,
+                                   smem_optin, 0, plan, nullptr);
+    plan->workspace_bytes = ws;
+    return rc;
+}
+
+int stream_forward(void* encode_fn_ptr, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r,
+                   int L, float eps, int* status_dev, cudaStream_t stream, int num_sms, int smem_optin,
+                   unsigned int spin_limit, unsigned long long* prof) {
+    return dispatch_stream(encode_fn_ptr, x, y, Vp, Up, M, d, r, L, eps, status_dev, stream, num_sms, smem_optin,
+                           spin_limit, nullptr, prof);
+}
+
+}  // namespace dlr

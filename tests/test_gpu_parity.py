@@ -212,7 +212,8 @@ def _cluster_case(D, d, r, L, M, seed, alpha, jitter=0.0):
 @pytest.mark.parametrize("d,r,M", [(512, 32, 128), (512, 64, 65), (512, 128, 200), (1024, 32, 130), (1024, 64, 65),
                                    (2048, 64, 384), (2048, 128, 200), (4096, 128, 129), (4096, 128, 700),
                                    (1024, 32, 1100)])
-def test_cluster_path_shapes(D, d, r, M):
+def test_cluster_path_shapes(D, d, r, M, monkeypatch):
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "2")
     p, x, y, Vf, Uf = _cluster_case(D, d, r, 5, M, seed=d + r + M, alpha=1.0, jitter=0.1)
     # same algebra with the activation re-rounded to bf16 after every layer (the bf16
     # transport of the partial z adds a little on top of this model)
@@ -262,3 +263,89 @@ def test_cluster_path_full_size_properties(D):
     assert O.rel_l2(y[rows].cpu(), y_small.cpu()) <= 1e-2
     assert O.rel_l2(y.cpu(), x.cpu()) > 1e-3          # the stack did move the activations
 
+
+
+# --------------------------------------------------------------------------- #
+# large-batch streamed path (one CTA per 128-row tile, activations streamed through L2)
+# --------------------------------------------------------------------------- #
+@pytest.mark.parametrize("d,r,L,M", [(512, 64, 3, 128), (512, 128, 2, 100), (1024, 128, 5, 300), (2048, 64, 7, 1000),
+                                     (1536, 64, 4, 257), (4096, 128, 3, 129), (640, 128, 3, 65)])
+def test_streamed_path_shapes(D, d, r, L, M, monkeypatch):
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "4")
+    p, x = O.seeded_case(d, r, L, M, seed=d + r + M, alpha=1.0, gain_jitter=0.1)
+    assert D.ops.query(M, d, r, L).path == 4
+    y, Vf, Uf = _run(D, p, x)
+    model = O.forward_folded_fp32(x, Vf, Uf, p.eps, round_h=True)   # activation re-rounded to bf16 after every layer
+    assert O.rel_l2(y, model) <= 6e-3
+    want = O.forward_fp32(x, p)
+    assert O.rel_l2(y, want) <= 1e-2
+    assert O.rel_l2_update(y, want, x) <= 5e-2
+
+
+@pytest.mark.parametrize("name", ["cfg2_d2048_r64", "cfg3_d4096_r128", "toy_d512_r64_stress"])
+def test_streamed_path_against_reference_fixtures(D, name, monkeypatch):
+    g = load_golden(name)
+    m = g["meta"]
+    p, x = O.seeded_case(m["d"], m["r"], m["L"], m["M"], m["seed"], m["alpha"], m["gain_jitter"])
+    reps = 65 // m["M"] + 1                      # the path takes more than 64 rows: repeat the fixture rows
+    xx = x.repeat(reps, 1)
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "4")
+    assert D.ops.query(xx.shape[0], m["d"], m["r"], m["L"]).path == 4
+    y, Vf, Uf = _run(D, p, xx)
+    for k in range(reps):                        # rows are independent: every copy gives the fixture's answer
+        yk = y[k * m["M"]:(k + 1) * m["M"]]
+        assert torch.equal(yk, y[:m["M"]])
+    y = y[:m["M"]]
+    assert O.rel_l2(y, g["y_bf16"]) <= TOL_TOTAL
+    assert O.rel_l2(y, g["y_fp32"]) <= TOL_TOTAL
+    assert O.rel_l2_update(y, g["y_bf16"], x) <= 0.3
+
+
+def test_streamed_path_is_chosen_where_it_is_faster_or_alone(D):
+    q = D.ops.query
+    assert q(8192, 4096, 128, 143).path == 2      # five cluster waves beat one streamed wave
+    assert q(12288, 4096, 128, 143).path == 4     # seven do not
+    assert q(4096, 8192, 128, 40).path == 4       # wider than a cluster of 8 can hold
+    assert q(8192, 1536, 64, 40).path == 4        # not a multiple of the cluster kernel's 512-column stripe
+    assert q(8192, 1024, 32, 141).path == 2       # rank 32 is not streamed
+    assert q(64, 4096, 128, 143).path == 1
+
+
+def test_streamed_path_several_tiles_per_cta_and_identity(D, monkeypatch):
+    # more tiles than SMs: CTAs walk several tiles; alpha = 0 must return the input bit for bit
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "4")
+    d, r, L, M = 512, 64, 3, 128 * 150 + 37
+    dev = torch.device("cuda:0")
+    p, x = O.seeded_case(d, r, L, 256, seed=11, alpha=1.0, gain_jitter=0.1)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    xx = torch.randn(M, d, device=dev, generator=gen).to(torch.bfloat16)
+    xx[-256:] = x.to(dev)
+    assert D.ops.query(M, d, r, L).passes == 2
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    y = D.ops.forward_folded(xx, Vf, Uf)
+    Vz, Uz = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), torch.zeros(L, device=dev))
+    y0 = D.ops.forward_folded(xx, Vz, Uz)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert torch.equal(y0, xx)
+    assert O.rel_l2(y[-256:].cpu(), O.forward_fp32(x, p)) <= 1e-2
+
+
+def test_streamed_path_reports_a_timeout_instead_of_hanging(D, monkeypatch):
+    # a spin limit far too small for the first weight tile to land: the kernel must give up, say so, and the
+    # next call (normal limit) must work
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "4")
+    p, x = O.seeded_case(1024, 128, 4, 200, seed=9, alpha=1.0, gain_jitter=0.1)
+    dev = torch.device("cuda:0")
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    monkeypatch.setenv("DLRB200_SPIN_LIMIT", "4")
+    D.ops.forward_folded(x.to(dev), Vf, Uf)
+    torch.cuda.synchronize()
+    with pytest.raises(D.ops._lib.DlrB200Error):
+        D.ops.check_status()
+    monkeypatch.delenv("DLRB200_SPIN_LIMIT")
+    y = D.ops.forward_folded(x.to(dev), Vf, Uf)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert O.rel_l2(y.cpu(), O.forward_fp32(x, p)) <= 1e-2
