@@ -293,7 +293,7 @@ def main():
     value = world * M * 1e3 / ms_step
 
     flops = 4.0 * L * M * d * r
-    launches_per_step = plan.passes
+    launches_per_step = plan.passes if plan.path == 1 else 1   # the striped path launches once per 64 rows
     kernel_ms = ms_step / launches_per_step
     timed_s = ms / 1e3
     peak_tf = peaks["tf_sustained"] if timed_s > 1.0 else peaks["tf_burst"]
@@ -301,13 +301,13 @@ def main():
     # DRAM traffic per launch: one ncu capture of a one-wave launch (profiles/) showed traffic equal to the
     # algorithmic bytes; weights exceed L2, so a launch of several waves re-reads them once per wave.
     tiles = (M + 127) // 128
-    waves = -(-tiles // max(1, plan.grid // max(1, plan.cluster))) if plan.path == 2 else plan.passes
+    waves = plan.passes          # cluster / streamed paths: waves of row tiles inside the one launch
     traffic = waves * 4.0 * L * d * r + 4.0 * M * d
     roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
                 "frac": achieved_tf / peak_tf, "traffic": traffic,
                 "traffic_note": "bytes per launch, scaled by waves from a one-wave ncu capture",
                 "peak_source": f"{peaks['source']} ({'sustained' if timed_s > 1.0 else 'burst'})",
-                "kernel": "cluster" if plan.path == 2 else "striped", "kernel_ms": kernel_ms,
+                "kernel": {1: "striped", 2: "cluster", 3: "cluster_small", 4: "streamed"}.get(plan.path, "?"), "kernel_ms": kernel_ms,
                 "frac_of_nominal_2250": achieved_tf / 2250.0}
 
     line = {

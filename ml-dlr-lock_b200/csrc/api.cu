@@ -183,30 +183,54 @@ int check_shape(int M, int d, int r, int L) {
 
 // Which path serves M rows.  The cluster path handles any M in 128-row tiles
 // once a tile's worth of rows makes the tensor-memory path pay off.
-// Large batches: the cluster kernel (activations resident in tensor memory, one
-// exchange per layer inside a cluster) or the streamed kernel (one CTA per
-// 128-row tile, no exchange, activations streamed through L2).  The cluster
-// kernel finishes a wave of tiles sooner but holds only one tile per cluster
-// (15 clusters of 8 on a B200 at d = 4096); the streamed kernel takes one tile
-// per SM.  Measured at d = 4096, r = 128, L = 143: 8192 rows 5.98 ms against
-// 6.73 ms, 9728 rows 7.15 against 6.73, 16384 rows 10.75 against 8.26, 19200 rows
-// 11.9 against 15.6 (two streamed waves).  A streamed wave costs about
-// 0.75 * (cluster size) cluster waves, at every width measured (1024, 2048, 4096).
-// Shapes the cluster kernel does not cover (d > 4096, d not a multiple of 512)
-// always stream: 3.7 ms against 27.6 ms on the striped kernel at d = 8192, M = 4096.
+// Large batches: the cluster kernel (activations resident in tensor memory, the
+// width split over a cluster of d/512 CTAs, one exchange per layer) or the
+// streamed kernel (whole rows per cluster of 1, 2 or 4 CTAs, activations
+// streamed through L2).  Both were timed on a B200 over widths 512..4096, ranks
+// 64 and 128 and 128..32768 rows; the choice below is a cost model fitted to
+// those times (microseconds):
+//   cluster kernel   waves * L * t_layer, t_layer = 8.2 (r = 128) or 6.3 (r = 64) whatever the width; it
+//                    holds one row tile per cluster, so 8192 rows at d = 4096 are five waves on 15 clusters
+//   streamed kernel  waves * (L + 1) * (chunks per CTA * 1.45 + exchange), exchange = 0 / 4 / 6 for a split of
+//                    1 / 2 / 4; 20 % more when more than 100 unsplit CTAs contend for L2
+// At d = 4096, r = 128, L = 143: 2048 rows 2.33 ms (cluster) against 2.59 ms, 4096 rows 3.54 against 2.61,
+// 8192 rows 5.89 against 3.98, 16384 rows 10.9 against 8.1, 19200 rows 11.8 against 15.5 (two streamed waves).
+// Shapes the cluster kernel does not cover (d > 4096, d not a multiple of 512, r > d / 32) always stream:
+// 3.7 ms against 27.6 ms on the striped kernel at d = 8192, M = 4096.
+struct RouteEntry {
+    int M, d, r, L, sms, streamed;
+};
+RouteEntry g_route[32];
+int g_route_n = 0;
+std::mutex g_route_mutex;
+
 bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
     const int forced = env_int("DLRB200_FORCE_PATH", 0);
     if (M <= 64 || !dlr::stream_supported(d, r)) return false;
     if (forced == DLRB200_PATH_STREAMED) return true;
     if (forced != 0) return false;
     if (!dlr::cluster_supported(d, r, L)) return true;
+    {   // the two plans below ask the driver for occupancy: remember the answer per shape
+        std::lock_guard<std::mutex> lock(g_route_mutex);
+        for (int i = 0; i < g_route_n; ++i) {
+            const RouteEntry& e = g_route[i];
+            if (e.M == M && e.d == d && e.r == r && e.L == L && e.sms == di.num_sms) return e.streamed != 0;
+        }
+    }
     dlrb200_plan pc, ps;
     std::memset(&pc, 0, sizeof(pc));
     std::memset(&ps, 0, sizeof(ps));
     if (dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, &pc) != DLRB200_OK) return true;
     if (dlr::stream_plan(M, d, r, L, di.num_sms, di.smem_optin, &ps) != DLRB200_OK) return false;
-    // (not calibrated for a cluster of one CTA, which has no exchange to lose time in)
-    return pc.cluster >= 2 && pc.passes >= 2 && 4 * pc.passes >= 3 * pc.cluster * ps.passes;
+    const double t_cluster = double(pc.passes) * L * (r >= 128 ? 8.2 : 6.3);
+    const double exchange = ps.cluster >= 4 ? 6.0 : (ps.cluster == 2 ? 4.0 : 0.0);
+    double t_stream = double(ps.passes) * (L + 1) * (double(d / 128 / ps.cluster) * 1.45 + exchange);
+    if (ps.cluster == 1 && ps.grid > 100) t_stream *= 1.2;
+    const bool streamed = t_stream < 0.97 * t_cluster;
+    std::lock_guard<std::mutex> lock(g_route_mutex);
+    g_route[g_route_n % 32] = RouteEntry{M, d, r, L, di.num_sms, streamed ? 1 : 0};
+    if (g_route_n < 32) ++g_route_n;
+    return streamed;
 }
 
 bool use_cluster_path(int M, int d, int r, int L) {
@@ -287,6 +311,8 @@ size_t dlrb200_workspace_bytes(int M, int d, int r, int L) {
     size_t need = striped_workspace_bytes(r);
     const size_t c = dlr::cluster_workspace_bytes(M, d, r, L);
     if (c > need) need = c;
+    const size_t st = dlr::stream_workspace_bytes(M, d, r);
+    if (st > need) need = st;
     return (need + 255) & ~size_t(255);
 }
 
@@ -331,7 +357,7 @@ int dlrb200_forward(const void* x, void* y, const void* Vp, const void* Up, int 
     if (use_stream_path(M, d, r, L, di) && dlr::stream_aligned(x, y)) {
         EncodeTiledFn enc = encode_fn();
         if (!enc) return DLRB200_ERR_CUDA;
-        rc = dlr::stream_forward(reinterpret_cast<void*>(enc), x, y, Vp, Up, M, d, r, L, eps, status_dev, st, di.num_sms,
+        rc = dlr::stream_forward(reinterpret_cast<void*>(enc), x, y, Vp, Up, M, d, r, L, eps, workspace, status_dev, st, di.num_sms,
                                  di.smem_optin, spin_limit(),
                                  env_int("DLRB200_PROFILE", 0) ? reinterpret_cast<unsigned long long*>(
                                                                      static_cast<uint8_t*>(workspace) + 256)

@@ -44,6 +44,7 @@
 //
 // All waits are bounded; a wait that gives up raises an abort flag, records a
 // status word and every role drains and leaves.
+#include <cstdlib>
 #include <cstring>
 
 #include "ptx.cuh"
@@ -87,6 +88,7 @@ struct SBars {
     uint64_t a_ready;         // 8 epilogue warps: the updated chunk (bf16) is in tensor memory
     uint64_t a_empty;         // V-MMA warp: the chunk has been read
     uint64_t z_full, s_ready;
+    uint64_t xchg_bar;        // sp > 1: the other CTAs of the cluster have published their partial z
     uint64_t ssq_bar;         // the 8 epilogue warps have published their halves of the sums of squares
     uint64_t drain[2];        // all tensor-core work of an MMA warp is complete (waited for before leaving)
     uint32_t tmem_slot;
@@ -99,7 +101,9 @@ struct SParams {
     __nv_bfloat16* y;
     int M, d, L;
     int nch;                  // chunks per row: d / 128
+    int sp;                   // CTAs (one cluster) that share a row tile, each with nch / sp of the chunks
     int num_tiles;
+    uint4* xchg;              // sp > 1: per-layer exchange of the partial z between the CTAs of a cluster
     float eps, inv_d;
     int* status;
     unsigned int spin_limit;
@@ -173,6 +177,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         mbar_init(smem_u32(&bars->z_full), 1);
         mbar_init(smem_u32(&bars->s_ready), kEpiWarps);
         mbar_init(smem_u32(&bars->ssq_bar), kEpiWarps);
+        mbar_init(smem_u32(&bars->xchg_bar), kEpiWarps * (p.sp > 1 ? p.sp - 1 : 1));
         mbar_init(smem_u32(&bars->drain[0]), 1);
         mbar_init(smem_u32(&bars->drain[1]), 1);
         bars->abort_flag = 0;
@@ -188,11 +193,19 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     }
     tc_fence_before();
     __syncthreads();
+    if (p.sp > 1) {            // the peers' barriers must exist before anyone signals them
+        cluster_arrive_release();
+        cluster_wait_acquire();
+    }
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_slot;
     const uint32_t hbuf_s = smem_u32(hbuf), ubuf_s = smem_u32(ubuf), vbuf_s = smem_u32(vbuf);
-    const int nch = p.nch;
-    const int my_tiles = (p.num_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+    const int sp = p.sp;
+    const int rank = sp > 1 ? int(cluster_ctarank()) : 0;
+    const int cl = int(blockIdx.x) / sp, ncl = int(gridDim.x) / sp;   // this cluster, clusters in the grid
+    const int nch = p.nch / sp;                                      // chunks of this CTA
+    const int col0 = rank * nch * kCW;                               // its first column
+    const int my_tiles = (p.num_tiles - cl + ncl - 1) / ncl;
 
     int err = 0;
     int err_layer = 0;
@@ -221,10 +234,10 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     const uint32_t bar = smem_u32(&bars->h_full[hp.st]);
                     const uint32_t dst = hbuf_s + hp.st * kHBytes;
                     const CUtensorMap* src = hq >= 1 ? &tmY : &tmX;
-                    const int m0 = (int(blockIdx.x) + ht * int(gridDim.x)) * kRowsS;
+                    const int m0 = (cl + ht * ncl) * kRowsS;
                     mbar_arrive_expect_tx(bar, kHBytes);
-                    tma_load_2d(dst, src, hc * kCW, m0, bar);
-                    tma_load_2d(dst + 16384, src, hc * kCW + 64, m0, bar);
+                    tma_load_2d(dst, src, col0 + hc * kCW, m0, bar);
+                    tma_load_2d(dst + 16384, src, col0 + hc * kCW + 64, m0, bar);
                     hph[hp.st] = int(hp.ph);
                     hp.step(kNH);
                     ++nh;
@@ -236,7 +249,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     const uint32_t dst = ubuf_s + up.st * C::U_BYTES;
                     mbar_arrive_expect_tx(bar, C::U_BYTES);
 #pragma unroll
-                    for (int t = 0; t < C::UT; ++t) tma_load_2d(dst + t * 16384, &tmU, 64 * t, uq * p.d + uc * kCW, bar);
+                    for (int t = 0; t < C::UT; ++t) tma_load_2d(dst + t * 16384, &tmU, 64 * t, uq * p.d + col0 + uc * kCW, bar);
                     uph[up.st] = int(up.ph);
                     up.step(NU);
                     ++nu;
@@ -247,8 +260,8 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     const uint32_t bar = smem_u32(&bars->v_full[vp.st]);
                     const uint32_t dst = vbuf_s + vp.st * C::V_BYTES;
                     mbar_arrive_expect_tx(bar, C::V_BYTES);
-                    tma_load_2d(dst, &tmV, vc * kCW, vq * R, bar);
-                    tma_load_2d(dst + C::V_TILE_BYTES, &tmV, vc * kCW + 64, vq * R, bar);
+                    tma_load_2d(dst, &tmV, col0 + vc * kCW, vq * R, bar);
+                    tma_load_2d(dst + C::V_TILE_BYTES, &tmV, col0 + vc * kCW + 64, vq * R, bar);
                     vph[vp.st] = int(vp.ph);
                     vp.step(NV);
                     ++nv;
@@ -463,7 +476,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 #pragma unroll
                             for (int i = 0; i < 8; ++i) rv[k][i] = __shfl_xor_sync(0xffffffffu, out[8 * k + i], k);
                         const int sq = lane & 3;
-                        const int qrow = (int(blockIdx.x) + t * int(gridDim.x)) * kRowsS + 32 * q4 + (lane & ~3);
+                        const int qrow = (cl + t * ncl) * kRowsS + 32 * q4 + (lane & ~3);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const int tt = sq ^ j;
@@ -475,7 +488,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                                 sv[i] = (tt & 2) ? hi : lo;
                             }
                             const int grow = qrow + j;
-                            if (grow < p.M) stg32(p.y + size_t(grow) * p.d + c * kCW + 64 * hh + 16 * tt, sv);
+                            if (grow < p.M) stg32(p.y + size_t(grow) * p.d + col0 + c * kCW + 64 * hh + 16 * tt, sv);
                         }
                         ew[7] += DLS_CLK() - t3;
                     }
@@ -484,6 +497,55 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 if (q + 1 < p.L) {
                     // ---- z(q+1) is complete after the V-MMA warp's last chunk: s = silu(z * rstd) -> tensor memory
                     const long long t0 = DLS_CLK();
+                    constexpr int NZ = R / 2;            // columns of z per thread
+                    constexpr int NQ = NZ / 8 + 1;       // 16-byte words a thread publishes: z as bf16 pairs, then its sum of squares
+                    if (!w.cta(smem_u32(&bars->z_full), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    tc_fence_after();
+                    float zf[NZ];
+#pragma unroll
+                    for (int g = 0; g < NZ / 32; ++g) {
+                        uint32_t zv[32];
+                        tmem_ld32(tl + kZCol + uint32_t(hh * NZ + 32 * g), zv);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) zf[32 * g + j] = __uint_as_float(zv[j]);
+                    }
+                    if (sp > 1) {
+                        // Every CTA of the cluster holds the partial z of its own columns.  Each publishes its
+                        // partial (rounded to bf16) and its partial sums of squares in global memory, signals the
+                        // others, and adds up all sp partials in rank order, its own rounded like the rest, so that
+                        // every CTA arrives at the same s.  Slots alternate with the layer's parity: a CTA can be at
+                        // most one layer ahead of a peer that still reads.
+                        const int et = int(threadIdx.x) - 128;
+                        uint4* mine = p.xchg + ((size_t(cl) * 2 + (c_z & 1u)) * sp + rank) * (NQ * 256) + et;
+#pragma unroll
+                        for (int k = 0; k < NZ / 8; ++k)
+                            mine[k * 256] = make_uint4(pack_bf16x2(zf[8 * k], zf[8 * k + 1]), pack_bf16x2(zf[8 * k + 2], zf[8 * k + 3]),
+                                                       pack_bf16x2(zf[8 * k + 4], zf[8 * k + 5]), pack_bf16x2(zf[8 * k + 6], zf[8 * k + 7]));
+                        mine[(NQ - 1) * 256] = make_uint4(__float_as_uint(ssq), 0u, 0u, 0u);
+                        __threadfence();
+                        __syncwarp();
+                        if (lane == 0)
+                            for (int o = 1; o < sp; ++o)
+                                mbar_arrive_remote(mapa(smem_u32(&bars->xchg_bar), uint32_t((rank + o) % sp)));
+                        if (!w.cluster(smem_u32(&bars->xchg_bar), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+#pragma unroll
+                        for (int j = 0; j < NZ; ++j) zf[j] = 0.f;
+                        float qs = 0.f;
+                        for (int o = 0; o < sp; ++o) {
+                            const uint4* src = p.xchg + ((size_t(cl) * 2 + (c_z & 1u)) * sp + o) * (NQ * 256) + et;
+#pragma unroll
+                            for (int k = 0; k < NZ / 8; ++k) {
+                                const uint4 v = __ldcg(src + k * 256);
+                                zf[8 * k] += bf16lo_to_f(v.x); zf[8 * k + 1] += bf16hi_to_f(v.x);
+                                zf[8 * k + 2] += bf16lo_to_f(v.y); zf[8 * k + 3] += bf16hi_to_f(v.y);
+                                zf[8 * k + 4] += bf16lo_to_f(v.z); zf[8 * k + 5] += bf16hi_to_f(v.z);
+                                zf[8 * k + 6] += bf16lo_to_f(v.w); zf[8 * k + 7] += bf16hi_to_f(v.w);
+                            }
+                            qs += __uint_as_float(__ldcg(src + (NQ - 1) * 256).x);
+                        }
+                        ssq = qs;
+                    }
                     ssqx[hh * kRowsS + er] = ssq;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->ssq_bar));
@@ -491,21 +553,14 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     const float tot = ssq + ssqx[(hh ^ 1) * kRowsS + er];
                     const float rstd = rsqrtf(tot * p.inv_d + p.eps);
                     ssq = 0.f;
-                    if (!w.cta(smem_u32(&bars->z_full), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                     ++c_z;
                     ew[2] += DLS_CLK() - t0;
-                    tc_fence_after();
-                    constexpr int NZ = R / 2;            // columns of z per thread
 #pragma unroll
                     for (int g = 0; g < NZ / 32; ++g) {
-                        uint32_t zv[32];
-                        tmem_ld32(tl + kZCol + uint32_t(hh * NZ + 32 * g), zv);
-                        tmem_wait_ld();
                         uint32_t sv[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            sv[j] = pack_bf16x2(silu_f(__uint_as_float(zv[2 * j]) * rstd),
-                                                silu_f(__uint_as_float(zv[2 * j + 1]) * rstd));
+                            sv[j] = pack_bf16x2(silu_f(zf[32 * g + 2 * j] * rstd), silu_f(zf[32 * g + 2 * j + 1] * rstd));
                         tmem_st16(tl + kSCol + uint32_t(hh * (NZ / 2) + 16 * g), sv);
                     }
                     tmem_wait_st();
@@ -534,30 +589,76 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
+    if (sp > 1) {              // no CTA may leave while a peer can still signal its barrier
+        cluster_arrive_release();
+        cluster_wait_acquire();
+    }
+}
+
+constexpr size_t kXchgOffset = 65536;    // the exchange slots start here in the workspace (profiling counters come first)
+constexpr size_t kXchgBytesPerCta = 2 * (128 / 16 + 1) * 256 * 16;   // two parities x 9 words x 256 threads, rank 128
+
+// CTAs that share a row tile: as many as keep every tile resident at once, so that small batches still
+// spread over the whole GPU.  Each CTA needs at least four chunks.
+int pick_split(int num_tiles, int nch, int num_sms) {
+    int forced = 0;
+    if (const char* e = getenv("DLRB200_STREAM_SPLIT")) forced = atoi(e);
+    for (int sp = 4; sp >= 2; sp >>= 1) {
+        if (forced && forced != sp) continue;
+        if (nch % sp == 0 && nch / sp >= 4 && num_tiles * sp <= num_sms - num_sms % sp) return sp;
+    }
+    return 1;
 }
 
 template <int R>
 int launch_stream(void* enc, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int L, float eps,
-                  int* status_dev, cudaStream_t stream, int num_sms, int smem_optin, unsigned int spin_limit,
-                  dlrb200_plan* plan_only, unsigned long long* prof) {
+                  void* workspace, int* status_dev, cudaStream_t stream, int num_sms, int smem_optin,
+                  unsigned int spin_limit, dlrb200_plan* plan_only, unsigned long long* prof) {
     using C = SCfg<R>;
     if (C::SMEM_BYTES > smem_optin) return DLRB200_ERR_OCCUPANCY;
     const int num_tiles = (M + kRowsS - 1) / kRowsS;
-    const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+    int sp = pick_split(num_tiles, d / kCW, num_sms);
+    auto kern = dlr_stream_kernel<R>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+        return DLRB200_ERR_CUDA;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    cfg.blockDim = dim3(kThreadsS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    int clusters = num_tiles < num_sms ? num_tiles : num_sms;
+    while (sp > 1) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = sp;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cfg.gridDim = dim3(sp * (num_sms / sp));
+        int max_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess) return DLRB200_ERR_CUDA;
+        if (max_clusters >= num_tiles) { clusters = num_tiles; break; }
+        sp >>= 1;                       // not all tiles resident at this split: use a smaller one
+    }
+    if (sp == 1) {
+        cfg.attrs = nullptr;
+        cfg.numAttrs = 0;
+        clusters = num_tiles < num_sms ? num_tiles : num_sms;
+    }
+    const int grid = clusters * sp;
+    cfg.gridDim = dim3(grid);
     if (plan_only) {
         plan_only->path = DLRB200_PATH_STREAMED;
         plan_only->grid = grid;
-        plan_only->cluster = 1;
+        plan_only->cluster = sp;
         plan_only->stripe_cols = kCW;
         plan_only->rows_per_pass = kRowsS;
-        plan_only->passes = (num_tiles + grid - 1) / grid;
+        plan_only->passes = (num_tiles + clusters - 1) / clusters;
         plan_only->stages = C::NU + C::NV;
         plan_only->smem_bytes = size_t(C::SMEM_BYTES);
         return DLRB200_OK;
     }
-    auto kern = dlr_stream_kernel<R>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-        return DLRB200_ERR_CUDA;
     CUtensorMap tmX, tmY, tmV, tmU;
     if (!encode_2d_bf16(enc, &tmX, x, uint64_t(d), uint64_t(M), 64, kRowsS, 128) ||
         !encode_2d_bf16(enc, &tmY, y, uint64_t(d), uint64_t(M), 64, kRowsS, 128) ||
@@ -569,22 +670,24 @@ int launch_stream(void* enc, const void* x, void* y, const void* Vp, const void*
     p.y = static_cast<__nv_bfloat16*>(y);
     p.M = M; p.d = d; p.L = L;
     p.nch = d / kCW;
+    p.sp = sp;
     p.num_tiles = num_tiles;
+    p.xchg = reinterpret_cast<uint4*>(static_cast<uint8_t*>(workspace) + kXchgOffset);
     p.eps = eps;
     p.inv_d = 1.0f / float(d);
     p.status = status_dev;
     p.spin_limit = spin_limit;
     p.prof = prof;
-    kern<<<grid, kThreadsS, C::SMEM_BYTES, stream>>>(tmX, tmY, tmV, tmU, p);
-    return cudaGetLastError() == cudaSuccess ? DLRB200_OK : DLRB200_ERR_CUDA;
+    const cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, tmX, tmY, tmV, tmU, p);
+    return ce == cudaSuccess ? DLRB200_OK : DLRB200_ERR_CUDA;
 }
 
 int dispatch_stream(void* enc, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r, int L,
-                    float eps, int* status_dev, cudaStream_t stream, int num_sms, int smem_optin,
+                    float eps, void* workspace, int* status_dev, cudaStream_t stream, int num_sms, int smem_optin,
                     unsigned int spin_limit, dlrb200_plan* plan_only, unsigned long long* prof) {
     switch (r) {
-        case 64: return launch_stream<64>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
-        case 128: return launch_stream<128>(enc, x, y, Vp, Up, M, d, L, eps, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
+        case 64: return launch_stream<64>(enc, x, y, Vp, Up, M, d, L, eps, workspace, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
+        case 128: return launch_stream<128>(enc, x, y, Vp, Up, M, d, L, eps, workspace, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
     }
     return DLRB200_ERR_UNSUPPORTED_SHAPE;
 }
@@ -602,16 +705,22 @@ bool stream_aligned(const void* x, const void* y) {
 
 int stream_plan(int M, int d, int r, int L, int num_sms, int smem_optin, dlrb200_plan* plan) {
     const size_t ws = plan->workspace_bytes;
-    const int rc = dispatch_stream(nullptr, nullptr, nullptr, nullptr, nullptr, M, d, r, L, 0.f, nullptr, nullptr, num_sms,
+    const int rc = dispatch_stream(nullptr, nullptr, nullptr, nullptr, nullptr, M, d, r, L, 0.f, nullptr, nullptr, nullptr, num_sms,
                                    smem_optin, 0, plan, nullptr);
     plan->workspace_bytes = ws;
     return rc;
 }
 
+size_t stream_workspace_bytes(int M, int d, int r) {
+    if (M <= 64 || !stream_supported(d, r)) return 0;
+    return kXchgOffset + 160 * kXchgBytesPerCta;    // one slot set per CTA, at most one CTA per SM
+}
+
 int stream_forward(void* encode_fn_ptr, const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r,
-                   int L, float eps, int* status_dev, cudaStream_t stream, int num_sms, int smem_optin,
+                   int L, float eps, void* workspace, int* status_dev, cudaStream_t stream, int num_sms, int smem_optin,
                    unsigned int spin_limit, unsigned long long* prof) {
-    return dispatch_stream(encode_fn_ptr, x, y, Vp, Up, M, d, r, L, eps, status_dev, stream, num_sms, smem_optin,
+    if (num_sms > 160) return DLRB200_ERR_OCCUPANCY;
+    return dispatch_stream(encode_fn_ptr, x, y, Vp, Up, M, d, r, L, eps, workspace, status_dev, stream, num_sms, smem_optin,
                            spin_limit, nullptr, prof);
 }
 

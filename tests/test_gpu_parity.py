@@ -303,11 +303,15 @@ def test_streamed_path_against_reference_fixtures(D, name, monkeypatch):
 
 def test_streamed_path_is_chosen_where_it_is_faster_or_alone(D):
     q = D.ops.query
-    assert q(8192, 4096, 128, 143).path == 2      # five cluster waves beat one streamed wave
-    assert q(12288, 4096, 128, 143).path == 4     # seven do not
+    assert q(1024, 4096, 128, 143).path == 2      # one cluster wave beats a streamed pass over the whole width
+    assert q(8192, 4096, 128, 143).path == 4      # five cluster waves do not beat one streamed wave of 64 pairs
+    assert q(8192, 4096, 128, 143).cluster == 2
+    assert q(4096, 4096, 128, 143).cluster == 4
+    assert q(19200, 4096, 128, 143).path == 2     # two streamed waves lose again
     assert q(4096, 8192, 128, 40).path == 4       # wider than a cluster of 8 can hold
     assert q(8192, 1536, 64, 40).path == 4        # not a multiple of the cluster kernel's 512-column stripe
     assert q(8192, 1024, 32, 141).path == 2       # rank 32 is not streamed
+    assert q(8192, 2048, 64, 142).path == 2
     assert q(64, 4096, 128, 143).path == 1
 
 
