@@ -187,14 +187,15 @@ int check_shape(int M, int d, int r, int L) {
 // width split over a cluster of d/512 CTAs, one exchange per layer) or the
 // streamed kernel (whole rows per cluster of 1, 2 or 4 CTAs, activations
 // streamed through L2).  Both were timed on a B200 over widths 512..4096, ranks
-// 64 and 128 and 128..32768 rows; the choice below is a cost model fitted to
+// 64 and 128 and 1024..32768 rows; the choice below is a cost model fitted to
 // those times (microseconds):
-//   cluster kernel   waves * L * t_layer, t_layer = 8.2 (r = 128) or 6.3 (r = 64) whatever the width; it
+//   cluster kernel   waves * L * t_layer, t_layer = 8.2 (r = 128) or 6.4 (r = 64) whatever the width; it
 //                    holds one row tile per cluster, so 8192 rows at d = 4096 are five waves on 15 clusters
-//   streamed kernel  waves * (L + 1) * (chunks per CTA * 1.45 + exchange), exchange = 0 / 4 / 6 for a split of
-//                    1 / 2 / 4; 20 % more when more than 100 unsplit CTAs contend for L2
-// At d = 4096, r = 128, L = 143: 2048 rows 2.33 ms (cluster) against 2.59 ms, 4096 rows 3.54 against 2.61,
-// 8192 rows 5.89 against 3.98, 16384 rows 10.9 against 8.1, 19200 rows 11.8 against 15.5 (two streamed waves).
+//   streamed kernel  waves * (L + 1) * (chunks per CTA * t_chunk + t_pass), t_chunk = 1.26 (r = 128) or 1.15
+//                    (r = 64), t_pass = 2.5 / 5.5 / 6.8 for a split of 1 / 2 / 4 (normalise + SiLU, and the
+//                    exchange); 30 % more when over 100 unsplit CTAs stream weights that do not fit in L2
+// At d = 4096, r = 128, L = 143: 2048 rows 2.34 ms (cluster) against 2.46 ms, 4096 rows 3.52 against 2.47,
+// 8192 rows 5.89 against 3.77, 16384 rows 10.6 against 7.8, 19200 rows 11.8 against 14.1 (two streamed waves).
 // Shapes the cluster kernel does not cover (d > 4096, d not a multiple of 512, r > d / 32) always stream:
 // 3.7 ms against 27.6 ms on the striped kernel at d = 8192, M = 4096.
 struct RouteEntry {
@@ -222,10 +223,10 @@ bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
     std::memset(&ps, 0, sizeof(ps));
     if (dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, &pc) != DLRB200_OK) return true;
     if (dlr::stream_plan(M, d, r, L, di.num_sms, di.smem_optin, &ps) != DLRB200_OK) return false;
-    const double t_cluster = double(pc.passes) * L * (r >= 128 ? 8.2 : 6.3);
-    const double exchange = ps.cluster >= 4 ? 6.0 : (ps.cluster == 2 ? 4.0 : 0.0);
-    double t_stream = double(ps.passes) * (L + 1) * (double(d / 128 / ps.cluster) * 1.45 + exchange);
-    if (ps.cluster == 1 && ps.grid > 100) t_stream *= 1.2;
+    const double t_cluster = double(pc.passes) * L * (r >= 128 ? 8.2 : 6.4);
+    const double t_pass = ps.cluster >= 4 ? 6.8 : (ps.cluster == 2 ? 5.5 : 2.5);
+    double t_stream = double(ps.passes) * (L + 1) * (double(d / 128 / ps.cluster) * (r >= 128 ? 1.26 : 1.15) + t_pass);
+    if (ps.cluster == 1 && ps.grid > 100 && 4.0 * L * d * r > 100e6) t_stream *= 1.3;
     const bool streamed = t_stream < 0.97 * t_cluster;
     std::lock_guard<std::mutex> lock(g_route_mutex);
     g_route[g_route_n % 32] = RouteEntry{M, d, r, L, di.num_sms, streamed ? 1 : 0};

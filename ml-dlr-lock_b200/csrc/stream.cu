@@ -17,30 +17,30 @@
 // core's rate that alone is the whole 128 B/clk of the shared-memory port.  So
 // as little else as possible goes through shared memory: both A operands (s
 // and the updated chunk) are bf16 in tensor memory (tcgen05.mma with A in
-// TMEM); the old values of a chunk come in by TMA (a thread owns a row, so
-// plain loads would touch 32 cache lines per instruction) and the new values
-// go straight from registers to global memory (L2 at these batch sizes), 32
-// bytes at a time.
+// TMEM).  The activations do pass through a staging slot: the old values of a
+// chunk come in by TMA, the epilogue threads update them in place, and a TMA
+// store writes the slot back (a thread owns a row, so plain loads and stores
+// would touch 32 cache lines per instruction, and an SM writes to L2 at only
+// about 32 bytes per clock: threads that store themselves stall on it).
 //
 // Per chunk c of layer l (steady state), 128 rows x 128 columns, on one of two
 // tensor-memory buffers of 128 columns:
 //   producer warp   TMA loads of the old chunk, of U'[l] rows of the chunk and
 //                   of V'[l+1] columns of the chunk into three rings
 //   U-MMA warp      dh = s(l) * U'[l][chunk]^T  -> buffer (fp32)
-//   epilogue warps  h_new = h_old + dh (fp32 add, rounded once to bf16): h_old
-//                   from shared memory, h_new to global memory and, packed
-//                   bf16, back into the buffer over the dh it came from;
-//                   running sum of squares per row
+//   epilogue warps  h_new = h_old + dh (fp32 add, rounded once to bf16), in
+//                   place in the staging slot and, packed bf16, into tensor
+//                   memory; running sum of squares per row
+//   store warp      TMA store of the slot to the output buffer
 //   V-MMA warp      z(l+1) += h_new[chunk] * V'[l+1][:, chunk]^T  (A = buffer)
 // After the last chunk z(l+1) is complete; the epilogue warps turn it into
 // s(l+1) = silu(z * rsqrt(sumsq / d + eps)), bf16, into tensor memory.
 //
 // Layer 0 is preceded by a pass that only feeds x to the V-MMA warp.  Passes
 // 0 and -1 read x, every pass >= 0 writes y and every pass >= 1 reads y, so x
-// is never modified.  A chunk written in one pass is read by TMA in the next:
-// the writers fence towards the async proxy before they release the staging
-// slot, and the producer acquires a later release of a slot before it asks
-// for the chunk.
+// is never modified.  A chunk stored in one pass is loaded again in the next:
+// the store warp counts the chunks whose bulk store is complete, and the
+// producer waits for that count before it asks for the chunk.
 //
 // All waits are bounded; a wait that gives up raises an abort flag, records a
 // status word and every role drains and leaves.
@@ -56,10 +56,10 @@ namespace {
 
 constexpr int kRowsS = 128;              // rows per tile
 constexpr int kCW = 128;                 // columns per chunk
-constexpr int kThreadsS = 384;           // 12 warps: producer, U-MMA, V-MMA, (tensor-memory owner), 8 epilogue
+constexpr int kThreadsS = 384;           // 12 warps: producer, U-MMA, V-MMA, store (owns tensor memory), 8 epilogue
 constexpr int kEpiWarps = 8;
 constexpr int kMaxW = 8;                 // most stages of a weight ring
-constexpr int kNH = 2;                   // old chunks in flight
+constexpr int kNH = 3;                   // staging slots for chunks of activations
 constexpr int kHBytes = 2 * 16384;       // one chunk: two tiles of 128 rows x 64 columns (128-byte swizzle)
 constexpr uint32_t kZCol = 0;            // tensor-memory columns: z accumulator (R columns)
 constexpr uint32_t kSCol = 128;          //   s, bf16 packed two per column (R/2 columns)
@@ -73,7 +73,7 @@ struct SCfg {
     static constexpr int V_TILE_BYTES = R * 128;         // V' tile: R rows x 64 K-columns
     static constexpr int V_BYTES = 2 * V_TILE_BYTES;
     static constexpr int NU = R == 128 ? 2 : 4;          // stages of the U' ring
-    static constexpr int NV = R == 128 ? 3 : 6;          // stages of the V' ring (held until the chunk is updated)
+    static constexpr int NV = R == 128 ? 2 : 4;          // stages of the V' ring
     static constexpr int SMEM_BYTES = kNH * kHBytes + NU * U_BYTES + NV * V_BYTES + 1024 /*sums of squares*/ + 512 /*barriers*/ +
                                       1024 /*alignment*/;
 };
@@ -82,7 +82,8 @@ struct SBars {
     uint64_t u_full[kMaxW], u_empty[kMaxW];
     uint64_t v_full[kMaxW], v_empty[kMaxW];
     uint64_t h_full[kNH];     // old chunk has landed (TMA bytes)
-    uint64_t h_empty[kNH];    // the 8 epilogue warps have read it
+    uint64_t h_written[kNH];  // the 8 epilogue warps have updated it in place
+    uint64_t h_empty[kNH];    // the store warp's bulk copy has read it
     uint64_t dh_full[2];      // U-MMA warp: dh of the chunk is in the buffer
     uint64_t dh_empty[2];     // 8 epilogue warps: dh has been read
     uint64_t a_ready;         // 8 epilogue warps: the updated chunk (bf16) is in tensor memory
@@ -93,6 +94,7 @@ struct SBars {
     uint64_t drain[2];        // all tensor-core work of an MMA warp is complete (waited for before leaving)
     uint32_t tmem_slot;
     int abort_flag;
+    unsigned int stored;      // chunks of this CTA (all tiles, all passes) whose bulk store is complete
 };
 static_assert(sizeof(SBars) <= 512, "barrier block");
 
@@ -111,19 +113,6 @@ struct SParams {
 };
 
 #define DLS_CLK() (p.prof ? clock64() : 0ll)
-
-// 32-byte global accesses: a thread owns 128 contiguous bytes of its row per chunk, so these move whole sectors.
-__device__ __forceinline__ void ldg32(const void* ptr, uint32_t (&v)[8]) {
-    asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "l"(ptr)
-                 : "memory");
-}
-__device__ __forceinline__ void stg32(void* ptr, const uint32_t (&v)[8]) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
-                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
-                 : "memory");
-}
 
 // Non-blocking test of an mbarrier phase (try_wait may suspend the thread for a while).
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
@@ -152,6 +141,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     float* ssqx = reinterpret_cast<float*>(vbuf + NV * C::V_BYTES);   // [2 halves][128 rows]
     SBars* bars = reinterpret_cast<SBars*>(ssqx + 2 * kRowsS);
     volatile int* abort_flag = &bars->abort_flag;
+    volatile unsigned int* stored = &bars->stored;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -166,7 +156,8 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
         for (int s = 0; s < kNH; ++s) {
             mbar_init(smem_u32(&bars->h_full[s]), 1);
-            mbar_init(smem_u32(&bars->h_empty[s]), kEpiWarps);
+            mbar_init(smem_u32(&bars->h_written[s]), kEpiWarps);
+            mbar_init(smem_u32(&bars->h_empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars->dh_full[b]), 1);
@@ -181,6 +172,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         mbar_init(smem_u32(&bars->drain[0]), 1);
         mbar_init(smem_u32(&bars->drain[1]), 1);
         bars->abort_flag = 0;
+        bars->stored = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmX);
         tma_prefetch_desc(&tmY);
@@ -228,9 +220,10 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             uint32_t idle = 0;
             while ((nu < total || nv < total || nh < total_h) && !err) {
                 bool did = false;
-                if (nh < total_h && mbar_test_wait(smem_u32(&bars->h_empty[hp.st]), hp.ph ^ 1u)) {
-                    // pass >= 1 reads what this CTA's epilogue threads stored one pass earlier; they fenced those
-                    // stores towards the async proxy before the release of a staging slot observed above
+                // pass >= 1 reads what this CTA stored one pass (nch chunks) earlier
+                if (nh < total_h && (hq < 1 || *stored + unsigned(nch) > unsigned(nh)) &&
+                    mbar_test_wait(smem_u32(&bars->h_empty[hp.st]), hp.ph ^ 1u)) {
+                    if (hq >= 1) asm volatile("fence.proxy.async.global;" ::: "memory");
                     const uint32_t bar = smem_u32(&bars->h_full[hp.st]);
                     const uint32_t dst = hbuf_s + hp.st * kHBytes;
                     const CUtensorMap* src = hq >= 1 ? &tmY : &tmX;
@@ -371,6 +364,40 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             mbar_wait(smem_u32(&bars->drain[1]), 0, kDrainPolls);
             if (p.prof) for (int k = 0; k < 2; ++k) p.prof[blockIdx.x * 32 + 8 + k] = (unsigned long long)mw[k];
         }
+    } else if (warp == 3) {
+        // =============================== store warp ================================
+        // updated chunk -> output buffer.  The slot is released when the copy has read it; the chunk counts as
+        // stored (readable by the next pass) once its bulk group is complete, which is checked two chunks late
+        // so that this warp never waits for a write in flight.
+        if (lane == 0) {
+            RingPos hp;
+            unsigned int n = 0;              // chunks seen (all tiles, all passes): the producer counts the same way
+            for (int t = 0; t < my_tiles && !err; ++t) {
+                const int m0 = (cl + t * ncl) * kRowsS;
+                for (int q = -1; q < p.L && !err; ++q) {
+                    err_layer = q;
+                    for (int c = 0; c < nch; ++c, ++n) {
+                        if (!w.cta(smem_u32(&bars->h_written[hp.st]), hp.ph)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        if (q >= 0) {
+                            const uint32_t src = hbuf_s + hp.st * kHBytes;
+                            tma_store_2d(&tmY, col0 + c * kCW, m0, src);
+                            tma_store_2d(&tmY, col0 + c * kCW + 64, m0, src + 16384);
+                            bulk_commit_group();
+                            bulk_wait_group_read<0>();
+                            bulk_wait_group<2>();            // every group but the last two is complete
+                            if (n + 1u > *stored + 2u) *stored = n + 1u - 2u;
+                        } else {
+                            // the pass over x stores nothing; also the point where the tile before is fully stored
+                            bulk_wait_group<0>();
+                            *stored = n + 1u;
+                        }
+                        mbar_arrive(smem_u32(&bars->h_empty[hp.st]));
+                        hp.step(kNH);
+                    }
+                }
+            }
+            bulk_wait_group<0>();
+        }
     } else if (warp >= 4) {
         // =============================== epilogue warps =============================
         // Two threads per row: thread (row er, half hh) owns 64 of the 128 columns of every chunk and half of
@@ -443,6 +470,19 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                             out[j] = cur[j];
                         }
                     }
+                    // ---- new values back into the staging slot, in place: the store warp copies the slot out
+                    const long long t3 = DLS_CLK();
+                    if (q >= 0) {
+                        uint8_t* rowp = hbuf + hp.st * kHBytes + hh * 16384 + er * 128;
+#pragma unroll
+                        for (int ch = 0; ch < 8; ++ch)
+                            *reinterpret_cast<uint4*>(rowp + ((uint32_t(ch) ^ x7) << 4)) =
+                                make_uint4(out[4 * ch], out[4 * ch + 1], out[4 * ch + 2], out[4 * ch + 3]);
+                        fence_async_smem();
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->h_written[hp.st]));
+                    ew[7] += DLS_CLK() - t3;
                     // ---- the chunk (bf16) becomes the A operand of the next layer's contraction
                     const long long t2 = DLS_CLK();
                     if (!w.cta(smem_u32(&bars->a_empty), (n & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
@@ -453,45 +493,9 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(smem_u32(&bars->h_empty[hp.st]));
-                        mbar_arrive(smem_u32(&bars->a_ready));
-                    }
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->a_ready));
                     hp.step(kNH);
                     ew[6] += DLS_CLK() - t2;
-                    if (q >= 0) {
-                        // ---- new values to global memory.  A thread holds 128 contiguous bytes of its own row, so a
-                        // plain store would touch 32 cache lines per instruction; the four lanes of a quad trade
-                        // sectors instead, and every store instruction then writes whole 128-byte lines (one row per
-                        // quad): in round k a lane receives sector k of row (lane ^ k), and instruction j stores, per
-                        // quad, row j of the quad, lane s storing sector s ^ j.
-                        const long long t3 = DLS_CLK();
-                        // the stores of the chunk before are long complete; the next pass reads them by TMA
-                        asm volatile("fence.proxy.async.global;" ::: "memory");
-                        uint32_t rv[4][8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) rv[0][i] = out[i];
-#pragma unroll
-                        for (int k = 1; k < 4; ++k)
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) rv[k][i] = __shfl_xor_sync(0xffffffffu, out[8 * k + i], k);
-                        const int sq = lane & 3;
-                        const int qrow = (cl + t * ncl) * kRowsS + 32 * q4 + (lane & ~3);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int tt = sq ^ j;
-                            uint32_t sv[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const uint32_t lo = (tt & 1) ? rv[1][i] : rv[0][i];
-                                const uint32_t hi = (tt & 1) ? rv[3][i] : rv[2][i];
-                                sv[i] = (tt & 2) ? hi : lo;
-                            }
-                            const int grow = qrow + j;
-                            if (grow < p.M) stg32(p.y + size_t(grow) * p.d + col0 + c * kCW + 64 * hh + 16 * tt, sv);
-                        }
-                        ew[7] += DLS_CLK() - t3;
-                    }
                 }
                 if (err) break;
                 if (q + 1 < p.L) {
@@ -694,13 +698,13 @@ int dispatch_stream(void* enc, const void* x, void* y, const void* Vp, const voi
 
 }  // namespace
 
-// The producer asks for a chunk up to two chunks ahead of the epilogue; a row of at least four chunks keeps
-// that well behind the stores of the pass before.
+// The store warp reports a chunk as stored two chunks late, and the producer runs up to three chunks ahead of
+// the epilogue: a CTA needs at least four chunks per pass for the next pass's first loads to be released.
 bool stream_supported(int d, int r) { return (r == 64 || r == 128) && d % kCW == 0 && d >= 4 * kCW; }
 
-// The epilogue moves the activations 32 bytes at a time.
+// The activations move by TMA: 16-byte aligned bases (rows are d * 2 bytes, a multiple of 256).
 bool stream_aligned(const void* x, const void* y) {
-    return (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
+    return (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0;
 }
 
 int stream_plan(int M, int d, int r, int L, int num_sms, int smem_optin, dlrb200_plan* plan) {

@@ -312,6 +312,8 @@ def test_streamed_path_is_chosen_where_it_is_faster_or_alone(D):
     assert q(8192, 1536, 64, 40).path == 4        # not a multiple of the cluster kernel's 512-column stripe
     assert q(8192, 1024, 32, 141).path == 2       # rank 32 is not streamed
     assert q(8192, 2048, 64, 142).path == 2
+    assert q(16384, 2048, 64, 142).path == 4
+    assert q(8192, 512, 64, 60).path == 2         # a cluster of one CTA has no exchange to lose time in
     assert q(64, 4096, 128, 143).path == 1
 
 
