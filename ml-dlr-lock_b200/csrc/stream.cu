@@ -527,7 +527,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                             mine[k * 256] = make_uint4(pack_bf16x2(zf[8 * k], zf[8 * k + 1]), pack_bf16x2(zf[8 * k + 2], zf[8 * k + 3]),
                                                        pack_bf16x2(zf[8 * k + 4], zf[8 * k + 5]), pack_bf16x2(zf[8 * k + 6], zf[8 * k + 7]));
                         mine[(NQ - 1) * 256] = make_uint4(__float_as_uint(ssq), 0u, 0u, 0u);
-                        __threadfence();
+                        // the arrive below releases these stores at cluster scope and the peers' wait acquires them
                         __syncwarp();
                         if (lane == 0)
                             for (int o = 1; o < sp; ++o)
@@ -564,7 +564,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                         uint32_t sv[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            sv[j] = pack_bf16x2(silu_f(zf[32 * g + 2 * j] * rstd), silu_f(zf[32 * g + 2 * j + 1] * rstd));
+                            sv[j] = pack_bf16x2(silu_tanh_f(zf[32 * g + 2 * j] * rstd), silu_tanh_f(zf[32 * g + 2 * j + 1] * rstd));
                         tmem_st16(tl + kSCol + uint32_t(hh * (NZ / 2) + 16 * g), sv);
                     }
                     tmem_wait_st();
