@@ -187,6 +187,93 @@ def cpu_forward_sampler(d, r, L, seed, rows):
     return lambda: O.forward_eager(x, p)
 
 
+def locked_decoder_loop(dev, batch=8, prompt=512, steps=256, eager_steps=2):
+    """The locked decoder loop on synthetic shapes: a randomly initialised Qwen3-shaped decoder (28 layers,
+    hidden 1024, 16 query / 8 key-value heads of 128, d_ff 3072, vocabulary 151936) whose MLPs are DLR-Nets of
+    rank 32 (depth 141), batch 8, 512 uniform-random prompt ids, 256 greedy steps on the KV cache.  Timed with
+    the CUDA library under the nets, and for a few steps with the torch layer loop under them (the
+    reference's own arithmetic: about 31000 kernel launches per token)."""
+    import time
+
+    from transformers import AutoConfig
+
+    import dlr_lock_b200 as D
+    torch.manual_seed(5)
+    cfg = AutoConfig.for_model("qwen3", vocab_size=151936, hidden_size=1024, intermediate_size=3072,
+                               num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                               max_position_embeddings=2048, tie_word_embeddings=True)
+    model = D.locked_model_from_config(cfg, rank=32, device=dev, alpha_init=0.01).eval()
+    ids = torch.randint(0, 151936, (batch, prompt), device=dev)
+
+    def run(n_steps):
+        # plain loop: the host framework's eager decode on a growing cache (host-bound: about 2 ms of
+        # Python per decoder layer)
+        with torch.no_grad():
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            out = model(ids, use_cache=True)
+            tok = out.logits[:, -1:].argmax(-1)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            past = out.past_key_values
+            for _ in range(n_steps):
+                out = model(tok, past_key_values=past, use_cache=True)
+                past = out.past_key_values
+                tok = out.logits[:, -1:].argmax(-1)
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+        return (t1 - t0) * 1e3, (t2 - t1) * 1e3 / max(1, n_steps)
+
+    def run_graph(n_steps):
+        # one decode step captured in a CUDA graph on a static KV cache, replayed n_steps times
+        from transformers import StaticCache
+        with torch.no_grad():
+            cache = StaticCache(config=model.config, max_cache_len=prompt + n_steps + 8)
+            out = model(ids, past_key_values=cache, use_cache=True, cache_position=torch.arange(prompt, device=dev))
+            tok = out.logits[:, -1:].argmax(-1).clone()
+            pos = torch.tensor([prompt], device=dev)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    model(tok, past_key_values=cache, use_cache=True, cache_position=pos)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                out = model(tok, past_key_values=cache, use_cache=True, cache_position=pos)
+                nxt = out.logits[:, -1:].argmax(-1)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(n_steps):
+                graph.replay()
+                tok.copy_(nxt)
+                pos.add_(1)
+            torch.cuda.synchronize()
+            return (time.perf_counter() - t0) * 1e3 / n_steps
+
+    D.set_fast_path(model, True)
+    run(2)                                    # warm-up: weights folded, workspaces allocated
+    pre_ms, step_ms = run(32)
+    try:
+        graph_ms = run_graph(steps)
+        graph_note = "one decode step captured in a CUDA graph on a static KV cache"
+    except Exception as e:                    # host framework without a capturable static cache
+        graph_ms, graph_note = None, f"not captured: {type(e).__name__}"
+    D.ops.check_status()
+    D.set_fast_path(model, False)
+    run(1)
+    pre_eager, step_eager = run(eager_steps)
+    del model
+    torch.cuda.empty_cache()
+    best = graph_ms if graph_ms is not None else step_ms
+    return {"config": f"qwen3-shaped random init, 28 layers, d=1024, r=32, L=141, batch {batch}, prompt {prompt}, {steps} greedy steps",
+            "prefill_ms": pre_ms, "prefill_tokens_per_s": batch * prompt / (pre_ms * 1e-3),
+            "decode_ms_per_step": best, "decode_tokens_per_s": batch / (best * 1e-3),
+            "decode_mode": graph_note, "decode_ms_per_step_plain_loop": step_ms,
+            "torch_loop": {"prefill_ms": pre_eager, "decode_ms_per_step": step_eager, "steps_timed": eager_steps},
+            "timing": "host clock around synchronised regions (the loop includes the host framework's attention and sampling)"}
+
+
 def cpu_baseline(d, r, L, seed, rows=512, budget_s=12.0):
     fn = cpu_forward_sampler(d, r, L, seed, rows)
     fn()
@@ -365,6 +452,8 @@ def main():
                         "TFLOPs": 4.0 * L * m * d * r / (lo * 1e-6) / 1e12})
         line["prefill_other"] = pre
         ops.check_status()
+        if args.workload == "cfg3":
+            line["locked_decoder"] = locked_decoder_loop(dev)
         line["cpu_baseline"] = cpu_baseline(d, r, L, seed)
 
     if rank == 0:

@@ -13,9 +13,11 @@ from .model import (  # noqa: F401
     dlrnet_config,
     dlrnet_param_count,
     load_dlrnet_weights,
+    locked_model_from_config,
     replace_layer_mlp,
     save_dlrnet_weights,
     set_checkpointing,
+    set_fast_path,
     write_config,
 )
 from . import ops, registry, sharding  # noqa: F401

@@ -214,6 +214,32 @@ def build_locked_model(model_name, rank, multiplier=1.0, state_dicts=None, devic
     return model
 
 
+def locked_model_from_config(config, rank, multiplier=1.0, device="cpu", torch_dtype=torch.bfloat16,
+                             alpha_init=0.0):
+    """A randomly initialised causal LM of ``config`` with every MLP replaced by a DLR-Net: what
+    ``build_locked_model`` returns, minus the checkpoint (no files, no network).  Used where only the
+    shapes matter: timing and parity of the whole decoder loop."""
+    from transformers import AutoModelForCausalLM
+
+    with torch.device(device):
+        model = AutoModelForCausalLM.from_config(config, dtype=torch_dtype)
+    d, d_ff = model.config.hidden_size, model.config.intermediate_size
+    depth = compute_depth(d, d_ff, rank, multiplier)
+    for li in range(len(model.model.layers)):
+        replace_layer_mlp(model, li, d, rank, depth, alpha_init=alpha_init)
+    return model
+
+
+def set_fast_path(model, enabled: bool) -> int:
+    """Switch every DLR-Net of ``model`` between the CUDA library and the torch layer loop."""
+    n = 0
+    for m in model.modules():
+        if isinstance(m, DLRNet):
+            m.fast = bool(enabled)
+            n += 1
+    return n
+
+
 def load_dlrnet_weights(model, checkpoint_dir, n_layers=None):
     """Read ``layerNN.pt`` files into the model's DLR-Nets (dlr_lock/model.py:232-248)."""
     n = len(model.model.layers) if n_layers is None else n_layers

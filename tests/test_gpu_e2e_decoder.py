@@ -1,0 +1,65 @@
+"""The locked decoder loop end to end: a randomly initialised Qwen3-shaped decoder whose MLPs are
+DLR-Nets (28 layers, hidden 1024, 16 query / 8 key-value heads of 128, rank 32, depth 141), run once
+through the CUDA library and once through the torch layer loop (dlr_lock/model.py:93-101 restated in
+dlr_lock_b200.model.DLRNet._forward_impl), the way examples/smoke_test.py:101-124 compares surgery
+results.  Logits are compared under teacher forcing: the prefill, then single-token steps fed with the
+torch path's greedy tokens, each path on its own KV cache.  Sampled ids of a random model are not
+compared: an argmax tie flips on a one-ulp difference.
+"""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm())
+
+
+def test_locked_decoder_prefill_and_decode_logits():
+    import dlr_lock_b200 as D
+    from transformers import AutoConfig
+
+    dev = "cuda:0"
+    torch.manual_seed(0)
+    cfg = AutoConfig.for_model("qwen3", vocab_size=8192, hidden_size=1024, intermediate_size=3072,
+                               num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                               max_position_embeddings=2048, tie_word_embeddings=True)
+    model = D.locked_model_from_config(cfg, rank=32, device=dev, alpha_init=0.01).eval()
+    assert D.set_fast_path(model, True) == 28
+    assert model.model.layers[0].mlp.dlrnet.depth == D.compute_depth(1024, 3072, 32) == 141
+    truth = copy.deepcopy(model).float()          # same bf16-rounded weights, everything computed in fp32
+    D.set_fast_path(truth, False)
+
+    ids = torch.randint(0, 8192, (2, 48), device=dev)
+    with torch.no_grad():
+        D.set_fast_path(model, False)
+        eager = model(ids, use_cache=True)
+        D.set_fast_path(model, True)
+        fast = model(ids, use_cache=True)
+        want = truth(ids, use_cache=True)
+        torch.cuda.synchronize()
+        D.ops.check_status()
+        # the library against the torch loop in bf16, and both against the fp32 model: the library must not
+        # be further from the truth than the reference arithmetic is
+        assert _rel(fast.logits, eager.logits) <= 3e-2
+        e_fast, e_eager = _rel(fast.logits, want.logits), _rel(eager.logits, want.logits)
+        assert e_fast <= 1.25 * e_eager + 2e-3, (e_fast, e_eager)
+        # near-ties of a random model flip on one ulp: most positions agree, not all
+        assert (fast.logits.argmax(-1) == eager.logits.argmax(-1)).float().mean().item() >= 0.85
+
+        pe, pf = eager.past_key_values, fast.past_key_values
+        tok = eager.logits[:, -1:].argmax(-1)
+        for _ in range(3):
+            D.set_fast_path(model, False)
+            oe = model(tok, past_key_values=pe, use_cache=True)
+            pe = oe.past_key_values
+            D.set_fast_path(model, True)
+            of = model(tok, past_key_values=pf, use_cache=True)
+            pf = of.past_key_values
+            torch.cuda.synchronize()
+            D.ops.check_status()
+            assert _rel(of.logits, oe.logits) <= 3e-2
+            tok = oe.logits[:, -1:].argmax(-1)

@@ -355,3 +355,29 @@ def test_streamed_path_reports_a_timeout_instead_of_hanging(D, monkeypatch):
     torch.cuda.synchronize()
     D.ops.check_status()
     assert O.rel_l2(y.cpu(), O.forward_fp32(x, p)) <= 1e-2
+
+
+def test_forward_can_be_captured_in_a_cuda_graph(D):
+    # a serving loop replays one captured decode step: the call must record no allocation or host
+    # synchronisation, and a replay on new input must give what a direct call gives
+    dev = torch.device("cuda:0")
+    for (d, r, L, M) in ((1024, 32, 9, 8), (4096, 128, 4, 3), (2048, 64, 3, 200)):
+        p, x = O.seeded_case(d, r, L, 2 * M, seed=d + M, alpha=1.0, gain_jitter=0.1)
+        Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+        xin = x[:M].to(dev).contiguous()
+        out = torch.empty_like(xin)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            D.ops.forward_folded(xin, Vf, Uf, out=out)          # warm-up on the capture stream
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            D.ops.forward_folded(xin, Vf, Uf, out=out)
+        xin.copy_(x[M:].to(dev))
+        graph.replay()
+        torch.cuda.synchronize()
+        want = D.ops.forward_folded(x[M:].to(dev).contiguous(), Vf, Uf)
+        torch.cuda.synchronize()
+        D.ops.check_status()
+        assert torch.equal(out, want)
