@@ -59,31 +59,43 @@ constexpr int kCW = 128;                 // columns per chunk
 constexpr int kThreadsS = 384;           // 12 warps: producer, U-MMA, V-MMA, store (owns tensor memory), 8 epilogue
 constexpr int kEpiWarps = 8;
 constexpr int kMaxW = 8;                 // most stages of a weight ring
-constexpr int kNH = 3;                   // staging slots for chunks of activations
+constexpr int kMaxNH = 3;                // most staging slots for chunks of activations
 constexpr int kHBytes = 2 * 16384;       // one chunk: two tiles of 128 rows x 64 columns (128-byte swizzle)
 constexpr uint32_t kZCol = 0;            // tensor-memory columns: z accumulator (R columns)
-constexpr uint32_t kSCol = 128;          //   s, bf16 packed two per column (R/2 columns)
-constexpr uint32_t kACol = 192;          //   the updated chunk, bf16 packed two per column (64 columns)
-constexpr uint32_t kBufCol = 256;        //   two dh accumulators of 128 columns
 
+// Tensor-memory columns and shared-memory stages per rank.  Up to rank 128 there is room for two dh
+// accumulators and a separate A operand: z [0,128) | s [128,192) | A [192,256) | dh0 [256,384) | dh1 [384,512).
+// Rank 256 fills the 512 columns with z [0,256) | s [256,384) | one buffer [384,512) that holds dh and then,
+// in place, the bf16 chunk (columns 0-31 of the buffer: chunk columns 0-63, columns 64-95: chunk columns
+// 64-127); U-MMA, epilogue and V-MMA of a chunk then run one after the other.
 template <int R>
 struct SCfg {
-    static constexpr int UT = R / 64;                    // U' tiles per chunk: 128 rows x 64 K-columns
+    static constexpr bool ONE_BUF = R == 256;
+    static constexpr uint32_t S_COL = ONE_BUF ? 256 : 128;
+    static constexpr uint32_t BUF_COL = ONE_BUF ? 384 : 256;
+    static constexpr uint32_t A_COL = ONE_BUF ? 384 : 192;
+    static constexpr int NH = ONE_BUF ? 2 : 3;           // staging slots for chunks of activations
+    // a U' stage: 128 rows x up to 128 K-columns (tiles of 64); a chunk takes USPC stages
+    static constexpr int USPC = R == 256 ? 2 : 1;
+    static constexpr int UT = R / 64 / USPC;             // tiles per stage
     static constexpr int U_BYTES = UT * 16384;
-    static constexpr int V_TILE_BYTES = R * 128;         // V' tile: R rows x 64 K-columns
-    static constexpr int V_BYTES = 2 * V_TILE_BYTES;
-    static constexpr int NU = R == 128 ? 2 : 4;          // stages of the U' ring
-    static constexpr int NV = R == 128 ? 2 : 4;          // stages of the V' ring
-    static constexpr int SMEM_BYTES = kNH * kHBytes + NU * U_BYTES + NV * V_BYTES + 1024 /*sums of squares*/ + 512 /*barriers*/ +
+    // a V' stage: tiles of R rows x 64 K-columns; a chunk (128 K-columns) takes VSPC stages
+    static constexpr int VSPC = R == 256 ? 2 : 1;
+    static constexpr int V_TILE_BYTES = R * 128;
+    static constexpr int VT = 2 / VSPC;                  // tiles per stage
+    static constexpr int V_BYTES = VT * V_TILE_BYTES;
+    static constexpr int NU = R == 256 ? 3 : (R == 128 ? 2 : 4);   // stages of the U' ring
+    static constexpr int NV = R == 256 ? 2 : (R == 128 ? 2 : 4);   // stages of the V' ring
+    static constexpr int SMEM_BYTES = NH * kHBytes + NU * U_BYTES + NV * V_BYTES + 1024 /*sums of squares*/ + 512 /*barriers*/ +
                                       1024 /*alignment*/;
 };
 
 struct SBars {
     uint64_t u_full[kMaxW], u_empty[kMaxW];
     uint64_t v_full[kMaxW], v_empty[kMaxW];
-    uint64_t h_full[kNH];     // old chunk has landed (TMA bytes)
-    uint64_t h_written[kNH];  // the 8 epilogue warps have updated it in place
-    uint64_t h_empty[kNH];    // the store warp's bulk copy has read it
+    uint64_t h_full[kMaxNH];     // old chunk has landed (TMA bytes)
+    uint64_t h_written[kMaxNH];  // the 8 epilogue warps have updated it in place
+    uint64_t h_empty[kMaxNH];    // the store warp's bulk copy has read it
     uint64_t dh_full[2];      // U-MMA warp: dh of the chunk is in the buffer
     uint64_t dh_empty[2];     // 8 epilogue warps: dh has been read
     uint64_t a_ready;         // 8 epilogue warps: the updated chunk (bf16) is in tensor memory
@@ -132,7 +144,8 @@ __global__ void __launch_bounds__(kThreadsS, 1)
 dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmU, SParams p) {
     using C = SCfg<R>;
-    constexpr uint32_t NU = C::NU, NV = C::NV;
+    constexpr uint32_t NU = C::NU, NV = C::NV, kNH = C::NH;
+    constexpr uint32_t kSCol = C::S_COL, kACol = C::A_COL, kBufCol = C::BUF_COL;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* hbuf = smem;
@@ -154,7 +167,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             mbar_init(smem_u32(&bars->v_full[s]), 1);
             mbar_init(smem_u32(&bars->v_empty[s]), 1);
         }
-        for (int s = 0; s < kNH; ++s) {
+        for (int s = 0; s < kMaxNH; ++s) {
             mbar_init(smem_u32(&bars->h_full[s]), 1);
             mbar_init(smem_u32(&bars->h_written[s]), kEpiWarps);
             mbar_init(smem_u32(&bars->h_empty[s]), 1);
@@ -209,16 +222,17 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         // The two rings advance independently: whichever has a free stage gets its next tile.
         if (lane == 0) {
             RingPos up, vp, hp;
-            int uph[kMaxW], vph[kMaxW], hph[kNH];   // parity of the last copy requested into each stage, -1: none
+            int uph[kMaxW], vph[kMaxW], hph[kMaxNH];   // parity of the last copy requested into each stage, -1: none
             for (int i = 0; i < kMaxW; ++i) uph[i] = vph[i] = -1;
-            for (int i = 0; i < kNH; ++i) hph[i] = -1;
-            const long long total = (long long)my_tiles * p.L * nch;          // tiles of each weight stream
+            for (int i = 0; i < kMaxNH; ++i) hph[i] = -1;
+            const long long total_u = (long long)my_tiles * p.L * nch * C::USPC;   // stages of each weight stream
+            const long long total_v = (long long)my_tiles * p.L * nch * C::VSPC;
             const long long total_h = (long long)my_tiles * (p.L + 1) * nch;  // chunks of activations
             long long nu = 0, nv = 0, nh = 0;
-            int uq = 0, uc = 0, vq = 0, vc = 0;
+            int uq = 0, uc = 0, vq = 0, vc = 0, us = 0, vs = 0;   // layer, chunk, stage within the chunk
             int ht = 0, hq = -1, hc = 0;
             uint32_t idle = 0;
-            while ((nu < total || nv < total || nh < total_h) && !err) {
+            while ((nu < total_u || nv < total_v || nh < total_h) && !err) {
                 bool did = false;
                 // pass >= 1 reads what this CTA stored one pass (nch chunks) earlier
                 if (nh < total_h && (hq < 1 || *stored + unsigned(nch) > unsigned(nh)) &&
@@ -237,28 +251,30 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     if (++hc == nch) { hc = 0; if (++hq == p.L) { hq = -1; ++ht; } }
                     did = true;
                 }
-                if (nu < total && mbar_test_wait(smem_u32(&bars->u_empty[up.st]), up.ph ^ 1u)) {
+                if (nu < total_u && mbar_test_wait(smem_u32(&bars->u_empty[up.st]), up.ph ^ 1u)) {
                     const uint32_t bar = smem_u32(&bars->u_full[up.st]);
                     const uint32_t dst = ubuf_s + up.st * C::U_BYTES;
                     mbar_arrive_expect_tx(bar, C::U_BYTES);
 #pragma unroll
-                    for (int t = 0; t < C::UT; ++t) tma_load_2d(dst + t * 16384, &tmU, 64 * t, uq * p.d + col0 + uc * kCW, bar);
+                    for (int t = 0; t < C::UT; ++t)
+                        tma_load_2d(dst + t * 16384, &tmU, 64 * (us * C::UT + t), uq * p.d + col0 + uc * kCW, bar);
                     uph[up.st] = int(up.ph);
                     up.step(NU);
                     ++nu;
-                    if (++uc == nch) { uc = 0; if (++uq == p.L) uq = 0; }
+                    if (++us == C::USPC) { us = 0; if (++uc == nch) { uc = 0; if (++uq == p.L) uq = 0; } }
                     did = true;
                 }
-                if (nv < total && mbar_test_wait(smem_u32(&bars->v_empty[vp.st]), vp.ph ^ 1u)) {
+                if (nv < total_v && mbar_test_wait(smem_u32(&bars->v_empty[vp.st]), vp.ph ^ 1u)) {
                     const uint32_t bar = smem_u32(&bars->v_full[vp.st]);
                     const uint32_t dst = vbuf_s + vp.st * C::V_BYTES;
                     mbar_arrive_expect_tx(bar, C::V_BYTES);
-                    tma_load_2d(dst, &tmV, col0 + vc * kCW, vq * R, bar);
-                    tma_load_2d(dst + C::V_TILE_BYTES, &tmV, col0 + vc * kCW + 64, vq * R, bar);
+#pragma unroll
+                    for (int t = 0; t < C::VT; ++t)
+                        tma_load_2d(dst + t * C::V_TILE_BYTES, &tmV, col0 + vc * kCW + 64 * (vs * C::VT + t), vq * R, bar);
                     vph[vp.st] = int(vp.ph);
                     vp.step(NV);
                     ++nv;
-                    if (++vc == nch) { vc = 0; if (++vq == p.L) vq = 0; }
+                    if (++vs == C::VSPC) { vs = 0; if (++vc == nch) { vc = 0; if (++vq == p.L) vq = 0; } }
                     did = true;
                 }
                 if (did) {
@@ -270,7 +286,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             }
             if (err || *abort_flag) {
                 // copies requested before giving up still land in this CTA's shared memory: wait for them
-                for (int i = 0; i < kNH; ++i)
+                for (int i = 0; i < int(kNH); ++i)
                     if (hph[i] >= 0) mbar_wait(smem_u32(&bars->h_full[i]), uint32_t(hph[i]), kDrainPolls);
                 for (int i = 0; i < int(NU); ++i)
                     if (uph[i] >= 0) mbar_wait(smem_u32(&bars->u_full[i]), uint32_t(uph[i]), kDrainPolls);
@@ -288,6 +304,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             uint32_t c_s = 0;
             long long mw[3] = {0, 0, 0};
             for (int t = 0; t < my_tiles && !err; ++t) {
+                if (C::ONE_BUF) n += uint32_t(nch);          // the pass over x goes through the one buffer too
                 for (int q = 0; q < p.L && !err; ++q) {
                     err_layer = q;
                     long long t0 = DLS_CLK();
@@ -296,24 +313,35 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     tc_fence_after();
                     mw[0] += DLS_CLK() - t0;
                     for (int c = 0; c < nch; ++c, ++n) {
-                        const uint32_t b = n & 1u;
+                        const uint32_t b = C::ONE_BUF ? 0u : (n & 1u);
                         t0 = DLS_CLK();
-                        if (!w.cta(smem_u32(&bars->u_full[up.st]), up.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
-                        const long long t1 = DLS_CLK();
-                        mw[1] += t1 - t0;
-                        if (!w.cta(smem_u32(&bars->dh_empty[b]), ((n >> 1) & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        mw[2] += DLS_CLK() - t1;
-                        tc_fence_after();
-                        const uint32_t acc = tmem_base + kBufCol + b * 128u;
-                        const uint32_t ub = ubuf_s + up.st * C::U_BYTES;
-#pragma unroll
-                        for (int k = 0; k < R / 16; ++k) {
-                            const uint64_t bdesc = umma_desc(ub + uint32_t(k / 4) * 16384u, 2u, 1024u) + uint64_t(2 * (k % 4));
-                            umma_ts(acc, tmem_base + kSCol + uint32_t(8 * k), bdesc, idesc_u, k ? 1u : 0u);
+                        // the accumulator is free: two of them, released by the epilogue once dh is read, or the one
+                        // buffer, released by the V-MMA warp once the chunk before has been read as its A operand
+                        if (C::ONE_BUF) {
+                            if (!w.cta(smem_u32(&bars->a_empty), (n & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        } else {
+                            if (!w.cta(smem_u32(&bars->dh_empty[b]), ((n >> 1) & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                         }
-                        umma_commit(smem_u32(&bars->u_empty[up.st]));
+                        mw[2] += DLS_CLK() - t0;
+                        const uint32_t acc = tmem_base + kBufCol + b * 128u;
+#pragma unroll
+                        for (int su = 0; su < C::USPC; ++su) {
+                            t0 = DLS_CLK();
+                            if (!w.cta(smem_u32(&bars->u_full[up.st]), up.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                            mw[1] += DLS_CLK() - t0;
+                            tc_fence_after();
+                            const uint32_t ub = ubuf_s + up.st * C::U_BYTES;
+                            constexpr int KS = R / 16 / C::USPC;      // K steps per stage
+#pragma unroll
+                            for (int k = 0; k < KS; ++k) {
+                                const uint64_t bdesc = umma_desc(ub + uint32_t(k / 4) * 16384u, 2u, 1024u) + uint64_t(2 * (k % 4));
+                                umma_ts(acc, tmem_base + kSCol + uint32_t(8 * (su * KS + k)), bdesc, idesc_u, (su | k) ? 1u : 0u);
+                            }
+                            umma_commit(smem_u32(&bars->u_empty[up.st]));
+                            up.step(NU);
+                        }
+                        if (err) break;
                         umma_commit(smem_u32(&bars->dh_full[b]));
-                        up.step(NU);
                     }
                 }
             }
@@ -338,20 +366,29 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                         if (!w.cta(smem_u32(&bars->a_ready), n & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                         mw[0] += DLS_CLK() - t0;
                         if (feeds) {
-                            t0 = DLS_CLK();
-                            if (!w.cta(smem_u32(&bars->v_full[vp.st]), vp.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
-                            mw[1] += DLS_CLK() - t0;
-                            tc_fence_after();
                             const uint32_t a0 = tmem_base + kACol;
-                            const uint32_t vb = vbuf_s + vp.st * C::V_BYTES;
 #pragma unroll
-                            for (int k = 0; k < kCW / 16; ++k) {
-                                const uint64_t bdesc = umma_desc(vb + uint32_t(k / 4) * C::V_TILE_BYTES, 2u, 1024u) + uint64_t(2 * (k % 4));
-                                umma_ts(tmem_base + kZCol, a0 + uint32_t(8 * k), bdesc, idesc_v, (c | k) ? 1u : 0u);
+                            for (int sv = 0; sv < C::VSPC; ++sv) {
+                                t0 = DLS_CLK();
+                                if (!w.cta(smem_u32(&bars->v_full[vp.st]), vp.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                                mw[1] += DLS_CLK() - t0;
+                                tc_fence_after();
+                                const uint32_t vb = vbuf_s + vp.st * C::V_BYTES;
+                                constexpr int KS = kCW / 16 / C::VSPC;    // K steps per stage
+#pragma unroll
+                                for (int kk = 0; kk < KS; ++kk) {
+                                    const int k = sv * KS + kk;          // K step of the chunk: 16 columns
+                                    const uint64_t bdesc = umma_desc(vb + uint32_t(kk / 4) * C::V_TILE_BYTES, 2u, 1024u) + uint64_t(2 * (kk % 4));
+                                    // the chunk as A operand: 8 columns per K step, contiguous, or in two runs of
+                                    // 32 columns where it shares the buffer with dh
+                                    const uint32_t acol = C::ONE_BUF ? uint32_t(64 * (k / 4) + 8 * (k % 4)) : uint32_t(8 * k);
+                                    umma_ts(tmem_base + kZCol, a0 + acol, bdesc, idesc_v, (c | k) ? 1u : 0u);
+                                }
+                                umma_commit(smem_u32(&bars->v_empty[vp.st]));
+                                vp.step(NV);
                             }
-                            umma_commit(smem_u32(&bars->v_empty[vp.st]));
+                            if (err) break;
                             umma_commit(smem_u32(&bars->a_empty));
-                            vp.step(NV);
                         } else {
                             mbar_arrive(smem_u32(&bars->a_empty));   // last layer: nothing reads the chunk here
                         }
@@ -418,7 +455,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             for (int q = -1; q < p.L && !err; ++q) {
                 err_layer = q;
                 for (int c = 0; c < nch; ++c, ++n) {
-                    const uint32_t b = nu & 1u;
+                    const uint32_t b = C::ONE_BUF ? 0u : (nu & 1u);
                     const uint32_t buf = tl + kBufCol + b * 128u + uint32_t(64 * hh);
                     // ---- old values of the chunk: this thread's 128 bytes of its row, from the staging slot
                     long long t0 = DLS_CLK();
@@ -436,7 +473,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     uint32_t out[32];
                     t0 = DLS_CLK();
                     if (q >= 0) {
-                        if (!w.cta(smem_u32(&bars->dh_full[b]), (nu >> 1) & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        if (!w.cta(smem_u32(&bars->dh_full[b]), (C::ONE_BUF ? nu : (nu >> 1)) & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                         ++nu;
                         ew[1] += DLS_CLK() - t0;
                         tc_fence_after();
@@ -455,10 +492,12 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                                 out[16 * g + j] = pack_bf16x2(f0, f1);
                             }
                         }
-                        // dh has been read: the U-MMA warp may overwrite the accumulator
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bars->dh_empty[b]));
+                        if (!C::ONE_BUF) {
+                            // dh has been read: the U-MMA warp may overwrite the accumulator
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&bars->dh_empty[b]));
+                        }
                         ew[0] += DLS_CLK() - t0;
                     } else {
                         // pass over x: the chunk goes to the tensor core as it is
@@ -488,8 +527,9 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     if (!w.cta(smem_u32(&bars->a_empty), (n & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                     ew[5] += DLS_CLK() - t2;
                     tc_fence_after();
-                    tmem_st16(tl + kACol + uint32_t(32 * hh), *reinterpret_cast<uint32_t(*)[16]>(&out[0]));
-                    tmem_st16(tl + kACol + uint32_t(32 * hh + 16), *reinterpret_cast<uint32_t(*)[16]>(&out[16]));
+                    constexpr uint32_t a_half = C::ONE_BUF ? 64u : 32u;   // in the shared buffer each thread writes over its own dh columns
+                    tmem_st16(tl + kACol + a_half * uint32_t(hh), *reinterpret_cast<uint32_t(*)[16]>(&out[0]));
+                    tmem_st16(tl + kACol + a_half * uint32_t(hh) + 16u, *reinterpret_cast<uint32_t(*)[16]>(&out[16]));
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
@@ -501,31 +541,30 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 if (q + 1 < p.L) {
                     // ---- z(q+1) is complete after the V-MMA warp's last chunk: s = silu(z * rstd) -> tensor memory
                     const long long t0 = DLS_CLK();
-                    constexpr int NZ = R / 2;            // columns of z per thread
+                    constexpr int NZ = R / 2;            // columns of z per thread, handled 32 at a time
                     constexpr int NQ = NZ / 8 + 1;       // 16-byte words a thread publishes: z as bf16 pairs, then its sum of squares
                     if (!w.cta(smem_u32(&bars->z_full), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                     tc_fence_after();
-                    float zf[NZ];
-#pragma unroll
-                    for (int g = 0; g < NZ / 32; ++g) {
-                        uint32_t zv[32];
-                        tmem_ld32(tl + kZCol + uint32_t(hh * NZ + 32 * g), zv);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) zf[32 * g + j] = __uint_as_float(zv[j]);
-                    }
+                    const int et = int(threadIdx.x) - 128;
                     if (sp > 1) {
                         // Every CTA of the cluster holds the partial z of its own columns.  Each publishes its
                         // partial (rounded to bf16) and its partial sums of squares in global memory, signals the
                         // others, and adds up all sp partials in rank order, its own rounded like the rest, so that
                         // every CTA arrives at the same s.  Slots alternate with the layer's parity: a CTA can be at
                         // most one layer ahead of a peer that still reads.
-                        const int et = int(threadIdx.x) - 128;
                         uint4* mine = p.xchg + ((size_t(cl) * 2 + (c_z & 1u)) * sp + rank) * (NQ * 256) + et;
 #pragma unroll
-                        for (int k = 0; k < NZ / 8; ++k)
-                            mine[k * 256] = make_uint4(pack_bf16x2(zf[8 * k], zf[8 * k + 1]), pack_bf16x2(zf[8 * k + 2], zf[8 * k + 3]),
-                                                       pack_bf16x2(zf[8 * k + 4], zf[8 * k + 5]), pack_bf16x2(zf[8 * k + 6], zf[8 * k + 7]));
+                        for (int g = 0; g < NZ / 32; ++g) {
+                            uint32_t zv[32];
+                            tmem_ld32(tl + kZCol + uint32_t(hh * NZ + 32 * g), zv);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float* f = reinterpret_cast<const float*>(&zv[8 * k]);
+                                mine[(4 * g + k) * 256] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                                                     pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+                            }
+                        }
                         mine[(NQ - 1) * 256] = make_uint4(__float_as_uint(ssq), 0u, 0u, 0u);
                         // the arrive below releases these stores at cluster scope and the peers' wait acquires them
                         __syncwarp();
@@ -533,21 +572,9 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                             for (int o = 1; o < sp; ++o)
                                 mbar_arrive_remote(mapa(smem_u32(&bars->xchg_bar), uint32_t((rank + o) % sp)));
                         if (!w.cluster(smem_u32(&bars->xchg_bar), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-#pragma unroll
-                        for (int j = 0; j < NZ; ++j) zf[j] = 0.f;
                         float qs = 0.f;
-                        for (int o = 0; o < sp; ++o) {
-                            const uint4* src = p.xchg + ((size_t(cl) * 2 + (c_z & 1u)) * sp + o) * (NQ * 256) + et;
-#pragma unroll
-                            for (int k = 0; k < NZ / 8; ++k) {
-                                const uint4 v = __ldcg(src + k * 256);
-                                zf[8 * k] += bf16lo_to_f(v.x); zf[8 * k + 1] += bf16hi_to_f(v.x);
-                                zf[8 * k + 2] += bf16lo_to_f(v.y); zf[8 * k + 3] += bf16hi_to_f(v.y);
-                                zf[8 * k + 4] += bf16lo_to_f(v.z); zf[8 * k + 5] += bf16hi_to_f(v.z);
-                                zf[8 * k + 6] += bf16lo_to_f(v.w); zf[8 * k + 7] += bf16hi_to_f(v.w);
-                            }
-                            qs += __uint_as_float(__ldcg(src + (NQ - 1) * 256).x);
-                        }
+                        for (int o = 0; o < sp; ++o)
+                            qs += __uint_as_float(__ldcg(p.xchg + ((size_t(cl) * 2 + (c_z & 1u)) * sp + o) * (NQ * 256) + et + (NQ - 1) * 256).x);
                         ssq = qs;
                     }
                     ssqx[hh * kRowsS + er] = ssq;
@@ -557,16 +584,38 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     const float tot = ssq + ssqx[(hh ^ 1) * kRowsS + er];
                     const float rstd = rsqrtf(tot * p.inv_d + p.eps);
                     ssq = 0.f;
-                    ++c_z;
                     ew[2] += DLS_CLK() - t0;
 #pragma unroll
                     for (int g = 0; g < NZ / 32; ++g) {
+                        float zf[32];
+                        if (sp > 1) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) zf[j] = 0.f;
+                            for (int o = 0; o < sp; ++o) {
+                                const uint4* src = p.xchg + ((size_t(cl) * 2 + (c_z & 1u)) * sp + o) * (NQ * 256) + et;
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const uint4 v = __ldcg(src + (4 * g + k) * 256);
+                                    zf[8 * k] += bf16lo_to_f(v.x); zf[8 * k + 1] += bf16hi_to_f(v.x);
+                                    zf[8 * k + 2] += bf16lo_to_f(v.y); zf[8 * k + 3] += bf16hi_to_f(v.y);
+                                    zf[8 * k + 4] += bf16lo_to_f(v.z); zf[8 * k + 5] += bf16hi_to_f(v.z);
+                                    zf[8 * k + 6] += bf16lo_to_f(v.w); zf[8 * k + 7] += bf16hi_to_f(v.w);
+                                }
+                            }
+                        } else {
+                            uint32_t zv[32];
+                            tmem_ld32(tl + kZCol + uint32_t(hh * NZ + 32 * g), zv);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) zf[j] = __uint_as_float(zv[j]);
+                        }
                         uint32_t sv[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            sv[j] = pack_bf16x2(silu_tanh_f(zf[32 * g + 2 * j] * rstd), silu_tanh_f(zf[32 * g + 2 * j + 1] * rstd));
+                            sv[j] = pack_bf16x2(silu_tanh_f(zf[2 * j] * rstd), silu_tanh_f(zf[2 * j + 1] * rstd));
                         tmem_st16(tl + kSCol + uint32_t(hh * (NZ / 2) + 16 * g), sv);
                     }
+                    ++c_z;
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
@@ -600,7 +649,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 }
 
 constexpr size_t kXchgOffset = 65536;    // the exchange slots start here in the workspace (profiling counters come first)
-constexpr size_t kXchgBytesPerCta = 2 * (128 / 16 + 1) * 256 * 16;   // two parities x 9 words x 256 threads, rank 128
+constexpr size_t kXchgBytesPerCta = 2 * (256 / 16 + 1) * 256 * 16;   // two parities x 17 words x 256 threads at rank 256
 
 // CTAs that share a row tile: as many as keep every tile resident at once, so that small batches still
 // spread over the whole GPU.  Each CTA needs at least four chunks.
@@ -692,6 +741,7 @@ int dispatch_stream(void* enc, const void* x, void* y, const void* Vp, const voi
     switch (r) {
         case 64: return launch_stream<64>(enc, x, y, Vp, Up, M, d, L, eps, workspace, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
         case 128: return launch_stream<128>(enc, x, y, Vp, Up, M, d, L, eps, workspace, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
+        case 256: return launch_stream<256>(enc, x, y, Vp, Up, M, d, L, eps, workspace, status_dev, stream, num_sms, smem_optin, spin_limit, plan_only, prof);
     }
     return DLRB200_ERR_UNSUPPORTED_SHAPE;
 }
@@ -700,7 +750,7 @@ int dispatch_stream(void* enc, const void* x, void* y, const void* Vp, const voi
 
 // The store warp reports a chunk as stored two chunks late, and the producer runs up to three chunks ahead of
 // the epilogue: a CTA needs at least four chunks per pass for the next pass's first loads to be released.
-bool stream_supported(int d, int r) { return (r == 64 || r == 128) && d % kCW == 0 && d >= 4 * kCW; }
+bool stream_supported(int d, int r) { return (r == 64 || r == 128 || r == 256) && d % kCW == 0 && d >= 4 * kCW; }
 
 // The activations move by TMA: 16-byte aligned bases (rows are d * 2 bytes, a multiple of 256).
 bool stream_aligned(const void* x, const void* y) {

@@ -269,7 +269,8 @@ def test_cluster_path_full_size_properties(D):
 # large-batch streamed path (one CTA per 128-row tile, activations streamed through L2)
 # --------------------------------------------------------------------------- #
 @pytest.mark.parametrize("d,r,L,M", [(512, 64, 3, 128), (512, 128, 2, 100), (1024, 128, 5, 300), (2048, 64, 7, 1000),
-                                     (1536, 64, 4, 257), (4096, 128, 3, 129), (640, 128, 3, 65)])
+                                     (1536, 64, 4, 257), (4096, 128, 3, 129), (640, 128, 3, 65),
+                                     (512, 256, 3, 128), (1024, 256, 4, 300), (5120, 256, 2, 700)])
 def test_streamed_path_shapes(D, d, r, L, M, monkeypatch):
     monkeypatch.setenv("DLRB200_FORCE_PATH", "4")
     p, x = O.seeded_case(d, r, L, M, seed=d + r + M, alpha=1.0, gain_jitter=0.1)
@@ -282,7 +283,7 @@ def test_streamed_path_shapes(D, d, r, L, M, monkeypatch):
     assert O.rel_l2_update(y, want, x) <= 5e-2
 
 
-@pytest.mark.parametrize("name", ["cfg2_d2048_r64", "cfg3_d4096_r128", "toy_d512_r64_stress"])
+@pytest.mark.parametrize("name", ["cfg2_d2048_r64", "cfg3_d4096_r128", "cfg4_d5120_r256", "toy_d512_r64_stress"])
 def test_streamed_path_against_reference_fixtures(D, name, monkeypatch):
     g = load_golden(name)
     m = g["meta"]
@@ -314,6 +315,7 @@ def test_streamed_path_is_chosen_where_it_is_faster_or_alone(D):
     assert q(8192, 2048, 64, 142).path == 2
     assert q(16384, 2048, 64, 142).path == 4
     assert q(8192, 512, 64, 60).path == 2         # a cluster of one CTA has no exchange to lose time in
+    assert q(4096, 5120, 256, 149).path == 4      # rank 256: one tensor-memory buffer, still streamed
     assert q(64, 4096, 128, 143).path == 1
 
 
