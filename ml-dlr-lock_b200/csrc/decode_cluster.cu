@@ -194,20 +194,34 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
     if (warp == 8) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
-            uint32_t n = 0;
+            // The V' tiles of a layer complete one barrier (that of the group's first stage), the U' tiles
+            // another: the compute warps wait twice per layer instead of once per tile (a wait on a landed tile
+            // still costs each of them about 200 cycles).  A stage's `full` barrier therefore advances only when
+            // the stage leads a group; `lead` holds its next parity per stage, and the compute warps keep the same
+            // bits.
             RingPos rp;
+            uint32_t lead = 0;
+            uint32_t last_bar[2] = {0, 0}, last_par[2] = {0, 0};   // the two youngest groups, for the drain below
+            bool any[2] = {false, false};
             for (l = 0; l < p.L && !err; ++l) {
-                for (int i = 0; i < kVT + C::UT; ++i, ++n, rp.step(uint32_t(S))) {
+                uint32_t bar = 0;
+                for (int i = 0; i < kVT + C::UT; ++i, rp.step(uint32_t(S))) {
                     const uint32_t st = rp.st;
                     if (!wait_cta(smem_u32(&bars->empty[st]), rp.ph ^ 1u)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
-                    const uint32_t bar = smem_u32(&bars->full[st]);
                     const uint32_t dst = ring_s + st * kStage;
+                    if (i == 0 || i == kVT) {
+                        const int grp = i == 0 ? 0 : 1;
+                        bar = smem_u32(&bars->full[st]);
+                        mbar_arrive_expect_tx(bar, i == 0 ? kVT * C::V_TILE_BYTES : C::UT * C::U_TILE_BYTES);
+                        last_bar[grp] = bar;
+                        last_par[grp] = (lead >> st) & 1u;
+                        any[grp] = true;
+                        lead ^= 1u << st;
+                    }
                     if (i < kVT) {
-                        mbar_arrive_expect_tx(bar, C::V_TILE_BYTES);
                         tma_load_2d(dst, &tmV, stripe0 + 64 * i, l * R, bar);
                     } else {
                         const int j = i - kVT;
-                        mbar_arrive_expect_tx(bar, C::U_TILE_BYTES);
                         tma_load_2d(dst, &tmU, (j % C::UK) * C::KW, l * p.d + stripe0 + 128 * (j / C::UK), bar);
                     }
                 }
@@ -217,11 +231,10 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
                     *abort_flag = 1;
                     atomicCAS(p.status, 0, err | (l << 8));
                 }
-                // tiles already requested still land in this CTA's ring: wait (bounded) before leaving
-                for (uint32_t back = 1; back <= uint32_t(S) && back <= n; ++back) {
-                    const uint32_t m = n - back;   // error path only: the division does not matter here
-                    mbar_wait(smem_u32(&bars->full[m % uint32_t(S)]), (m / uint32_t(S)) & 1u, kDrainPolls);
-                }
+                // tiles already requested still land in this CTA's ring: wait (bounded) before leaving.  A group
+                // cut short by the error never completes its byte count; older groups have been consumed.
+                for (int g = 0; g < 2; ++g)
+                    if (any[g]) mbar_wait(last_bar[g], last_par[g], kDrainPolls);
             }
         }
     } else {
@@ -248,6 +261,7 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
         const int urow = tid & 127;                            // this thread's row inside a U tile
         const int urb = tid >> 7;                              // which 128-row block of the U slice
         RingPos rp;
+        uint32_t lead = 0;                   // next parity of each stage's `full` barrier (see the producer)
         bool ok = true;
         long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #define DC_CLK() (p.prof ? clock64() : 0ll)
@@ -266,10 +280,9 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
             const float4 hb1 = *reinterpret_cast<const float4*>(hs + kSC + kcol0 + 4);
             uint32_t vst[kVT];
 #pragma unroll
-            for (int kt = 0; kt < kVT; ++kt, rp.step(uint32_t(S))) {
-                vst[kt] = rp.st;
-                ok = wait_cta(smem_u32(&bars->full[rp.st]), rp.ph) && ok;
-            }
+            for (int kt = 0; kt < kVT; ++kt, rp.step(uint32_t(S))) vst[kt] = rp.st;
+            ok = wait_cta(smem_u32(&bars->full[vst[0]]), (lead >> vst[0]) & 1u) && ok;   // all V' tiles of the layer
+            lead ^= 1u << vst[0];
             { const long long qq = DC_CLK(); pc[5] += qq - q0c; }
             float v[C::NV];
 #pragma unroll
@@ -345,11 +358,12 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
 
             // ---- U phase: column `tid` of the stripe: dot of its U' row with s, both token rows
             float d0 = 0.f, d1 = 0.f;
+            ok = wait_cta(smem_u32(&bars->full[rp.st]), (lead >> rp.st) & 1u) && ok;            // all U' tiles of the layer
+            lead ^= 1u << rp.st;
 #pragma unroll 1
             for (int j = 0; j < C::UT; ++j, rp.step(uint32_t(S))) {
                 const int rb = j / C::UK, kh = j % C::UK;
                 const uint32_t st = rp.st;
-                ok = wait_cta(smem_u32(&bars->full[st]), rp.ph) && ok;
                 if (ok && rb == urb) {
                     const uint8_t* tptr = ring + size_t(st) * kStage;
 #pragma unroll
