@@ -421,14 +421,45 @@ def main():
             jt[0] += 1
             ops.forward_host(xh[i], yh[i], xs[i], ys[i], Vp, Up)
 
-        ms_h = time_steps(step_host, args.steps, 3, barrier)
+        # (1) one stream: H2D, kernel, D2H of a step strictly one after the other
+        ms_serial = time_steps(step_host, args.steps, 3, barrier)
+        # (2) two streams, steps alternate: each step is still H2D -> kernel -> D2H on its own stream and its own
+        # buffers, but the copies of one step overlap the kernel of the other (what a serving loop does)
+        side = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
+
+        def run_piped(n):
+            for k in range(n):
+                with torch.cuda.stream(side[k & 1]):
+                    ops.forward_host(xh[k & 1], yh[k & 1], xs[k & 1], ys[k & 1], Vp, Up)
+
+        for st in side:
+            st.wait_stream(torch.cuda.current_stream())
+        run_piped(4)
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        torch.cuda.synchronize()
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ea.record()
+        for st in side:
+            st.wait_stream(torch.cuda.current_stream())
+        run_piped(args.steps)
+        for st in side:
+            torch.cuda.current_stream().wait_stream(st)
+        eb.record()
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        ms_h = ea.elapsed_time(eb)
         if world > 1:
-            t = torch.tensor([ms_h], device=dev, dtype=torch.float64)
+            t = torch.tensor([ms_h, ms_serial], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_h = float(t.item())
+            ms_h, ms_serial = float(t[0].item()), float(t[1].item())
         line["e2e"] = {"value": world * M * args.steps * 1e3 / ms_h, "unit": "tokens/s",
                        "h2d_bytes_per_step": M * d * 2, "d2h_bytes_per_step": M * d * 2,
-                       "ms_per_step": ms_h / args.steps}
+                       "ms_per_step": ms_h / args.steps,
+                       "mode": "dlrb200_forward_host from pinned host buffers, steps alternating between two streams",
+                       "one_stream": {"value": world * M * args.steps * 1e3 / ms_serial, "ms_per_step": ms_serial / args.steps}}
         ops.check_status()
 
     # ---- small-batch latencies and other prefill sizes (rank 0, N=1 only)

@@ -1,8 +1,8 @@
-// Large-batch ("prefill") DLR-Net forward, streamed path: one CTA walks one
-// 128-row tile of the batch through all L layers and the whole width d.  The
-// activations stream through registers and tensor memory chunk by chunk, in
-// place in the output buffer; shared memory holds nothing but weights, and no
-// CTA ever waits for another.
+// Large-batch ("prefill") DLR-Net forward, streamed path: one CTA (or a cluster
+// of 2 or 4 that share the width) walks one 128-row tile of the batch through
+// all L layers.  The activations stream chunk by chunk through a staging slot
+// in shared memory and through tensor memory, in place in the output buffer;
+// no cluster ever waits for another.
 //
 // Why.  Rows are independent (dlr_lock/model.py:96-100 acts on each token
 // alone), so a CTA that owns whole rows needs no exchange.  A tile of 128 rows
@@ -24,7 +24,7 @@
 // about 32 bytes per clock: threads that store themselves stall on it).
 //
 // Per chunk c of layer l (steady state), 128 rows x 128 columns, on one of two
-// tensor-memory buffers of 128 columns:
+// tensor-memory accumulators of 128 columns (one at rank 256, see SCfg):
 //   producer warp   TMA loads of the old chunk, of U'[l] rows of the chunk and
 //                   of V'[l+1] columns of the chunk into three rings
 //   U-MMA warp      dh = s(l) * U'[l][chunk]^T  -> buffer (fp32)
@@ -41,6 +41,11 @@
 // is never modified.  A chunk stored in one pass is loaded again in the next:
 // the store warp counts the chunks whose bulk store is complete, and the
 // producer waits for that count before it asks for the chunk.
+//
+// Split.  When there are fewer tiles than SMs, a cluster of sp = 2 or 4 CTAs
+// shares a tile: each takes d / 128 / sp chunks, and once per layer they add
+// up their partial z and partial sums of squares (published in global memory,
+// signalled with one remote mbarrier arrive per warp).
 //
 // All waits are bounded; a wait that gives up raises an abort flag, records a
 // status word and every role drains and leaves.
