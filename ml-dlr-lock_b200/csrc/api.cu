@@ -239,7 +239,11 @@ bool use_cluster_path(int M, int d, int r, int L) {
     if (forced == DLRB200_PATH_STRIPED || forced == DLRB200_PATH_STREAMED || forced == DLRB200_PATH_CLUSTER_SMALL) return false;
     if (!dlr::cluster_supported(d, r, L)) return false;
     if (forced == DLRB200_PATH_CLUSTER) return true;
-    return M > 64;
+    // One 128-row tile on one cluster costs the same for any M <= 128 (1.18 ms at d = 4096, r = 128, L = 143;
+    // 0.89 ms at d = 2048, r = 64, L = 142), while the striped kernel grows with M (0.43 + 0.0155 M ms and
+    // 0.51 + 0.0072 M ms): from about 52 rows on, the padded tile is the faster way.
+    if (M > 64) return true;
+    return M >= 52 && d >= 2048;
 }
 
 // Small batches: the cluster kernel (one cluster per pair of rows, exchange in

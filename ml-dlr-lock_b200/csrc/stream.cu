@@ -451,7 +451,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         uint32_t n = 0;                      // chunks seen (all passes): phase of the A operand's barriers
         uint32_t nu = 0;                     // chunks of update passes: accumulator nu & 1
         uint32_t c_z = 0;
-        long long ew[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long ew[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 
         RingPos hp;
         const uint32_t x7 = uint32_t(er & 7);
@@ -550,6 +550,8 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     constexpr int NQ = NZ / 8 + 1;       // 16-byte words a thread publishes: z as bf16 pairs, then its sum of squares
                     if (!w.cta(smem_u32(&bars->z_full), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                     tc_fence_after();
+                    const long long tb1 = DLS_CLK();
+                    ew[8] += tb1 - t0;
                     const int et = int(threadIdx.x) - 128;
                     if (sp > 1) {
                         // Every CTA of the cluster holds the partial z of its own columns.  Each publishes its
@@ -576,16 +578,21 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                         if (lane == 0)
                             for (int o = 1; o < sp; ++o)
                                 mbar_arrive_remote(mapa(smem_u32(&bars->xchg_bar), uint32_t((rank + o) % sp)));
+                        const long long tb2 = DLS_CLK();
+                        ew[9] += tb2 - tb1;
                         if (!w.cluster(smem_u32(&bars->xchg_bar), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        ew[10] += DLS_CLK() - tb2;
                         float qs = 0.f;
                         for (int o = 0; o < sp; ++o)
                             qs += __uint_as_float(__ldcg(p.xchg + ((size_t(cl) * 2 + (c_z & 1u)) * sp + o) * (NQ * 256) + et + (NQ - 1) * 256).x);
                         ssq = qs;
                     }
+                    const long long tb3 = DLS_CLK();
                     ssqx[hh * kRowsS + er] = ssq;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->ssq_bar));
                     if (!w.cta(smem_u32(&bars->ssq_bar), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    ew[11] += DLS_CLK() - tb3;
                     const float tot = ssq + ssqx[(hh ^ 1) * kRowsS + er];
                     const float rstd = rsqrtf(tot * p.inv_d + p.eps);
                     ssq = 0.f;
@@ -630,7 +637,7 @@ dlr_stream_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             }
         }
         if (p.prof && threadIdx.x == 128)
-            for (int k = 0; k < 8; ++k) p.prof[blockIdx.x * 32 + 12 + k] = (unsigned long long)ew[k];
+            for (int k = 0; k < 12; ++k) p.prof[blockIdx.x * 32 + 12 + k] = (unsigned long long)ew[k];
     }
 
     // ---- leave: report, let every role arrive, free tensor memory

@@ -270,7 +270,8 @@ def test_cluster_path_full_size_properties(D):
 # --------------------------------------------------------------------------- #
 @pytest.mark.parametrize("d,r,L,M", [(512, 64, 3, 128), (512, 128, 2, 100), (1024, 128, 5, 300), (2048, 64, 7, 1000),
                                      (1536, 64, 4, 257), (4096, 128, 3, 129), (640, 128, 3, 65),
-                                     (512, 256, 3, 128), (1024, 256, 4, 300), (5120, 256, 2, 700)])
+                                     (512, 256, 3, 128), (1024, 256, 4, 300), (5120, 256, 2, 700),
+                                     (512, 64, 1, 130), (1024, 128, 1, 65), (2048, 128, 2, 90)])
 def test_streamed_path_shapes(D, d, r, L, M, monkeypatch):
     monkeypatch.setenv("DLRB200_FORCE_PATH", "4")
     p, x = O.seeded_case(d, r, L, M, seed=d + r + M, alpha=1.0, gain_jitter=0.1)
@@ -316,7 +317,8 @@ def test_streamed_path_is_chosen_where_it_is_faster_or_alone(D):
     assert q(16384, 2048, 64, 142).path == 4
     assert q(8192, 512, 64, 60).path == 2         # a cluster of one CTA has no exchange to lose time in
     assert q(4096, 5120, 256, 149).path == 4      # rank 256: one tensor-memory buffer, still streamed
-    assert q(64, 4096, 128, 143).path == 1
+    assert q(40, 4096, 128, 143).path == 1
+    assert q(64, 4096, 128, 143).path == 2        # from about 52 rows a padded 128-row tile beats the striped kernel
 
 
 def test_streamed_path_several_tiles_per_cta_and_identity(D, monkeypatch):
