@@ -187,6 +187,32 @@ def cpu_forward_sampler(d, r, L, seed, rows):
     return lambda: O.forward_eager(x, p)
 
 
+def torch_loop_same_box(x, Vp, Up, eps=1e-6):
+    """The layer loop in eager torch ops on the same GPU, on the folded weights (the arithmetic of
+    dlr_lock/model.py:96-100 with the gain and alpha pre-multiplied: about six launches per layer).  A
+    comparison figure only: nothing of the product path runs here."""
+    import torch.nn.functional as F
+
+    def fwd():
+        h = x
+        for l in range(Vp.shape[0]):
+            rstd = torch.rsqrt(h.float().pow(2).mean(dim=-1, keepdim=True) + eps).to(h.dtype)
+            h = h + F.silu((h * rstd) @ Vp[l].T) @ Up[l].T
+        return h
+
+    with torch.no_grad():
+        fwd()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            fwd()
+        b.record()
+        torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 3
+    return {"ms_per_step": ms, "tokens_per_s": x.shape[0] / (ms * 1e-3), "what": "eager torch bf16 layer loop on folded weights, same GPU, same input"}
+
+
 def locked_decoder_loop(dev, batch=8, prompt=512, steps=256, eager_steps=2):
     """The locked decoder loop on synthetic shapes: a randomly initialised Qwen3-shaped decoder (28 layers,
     hidden 1024, 16 query / 8 key-value heads of 128, d_ff 3072, vocabulary 151936) whose MLPs are DLR-Nets of
@@ -483,6 +509,7 @@ def main():
                         "TFLOPs": 4.0 * L * m * d * r / (lo * 1e-6) / 1e12})
         line["prefill_other"] = pre
         ops.check_status()
+        line["same_box_torch_loop"] = torch_loop_same_box(xs[0], Vp, Up)
         if args.workload == "cfg3":
             line["locked_decoder"] = locked_decoder_loop(dev)
         line["cpu_baseline"] = cpu_baseline(d, r, L, seed)

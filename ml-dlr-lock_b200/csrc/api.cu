@@ -76,13 +76,17 @@ int env_int(const char* name, int dflt) {
 
 bool supported_rank(int r) { return r == 16 || r == 32 || r == 64 || r == 128 || r == 256; }
 
-// Stripe width of the small-batch path: the narrowest of 16/32/64 columns whose
-// stripe count fits one CTA per SM (all CTAs must be co-resident).
+// Stripe width of the small-batch path.  Every CTA adds its partial z into the same accumulator words, so
+// the exchange costs L2 atomics in proportion to the number of stripes: wide stripes win as long as a CTA
+// can still pull its share of the weights in time.  Measured at M = 1 / 8 (us): d = 4096: 310 / 432 with 64
+// columns against 418 / 664 with 32; d = 2048: 277 / 325 against 269 / 361; d = 1024: 271 / 302 (64), 263 / 296
+// (32), 258 / 320 (16).  All CTAs must be co-resident (one per SM).
 int pick_stripe_cols(int d, int num_sms) {
     const int forced = env_int("DLRB200_STRIPE_COLS", 0);
     if (forced == 16 || forced == 32 || forced == 64) return (d % forced == 0) ? forced : 0;
-    for (int dc : {16, 32, 64})
-        if (d % dc == 0 && d / dc <= num_sms) return dc;
+    const int want = d >= 2048 ? 64 : 32;
+    for (int dc : {64, 32, 16})
+        if (dc <= want && d % dc == 0 && d / dc <= num_sms) return dc;
     return 0;
 }
 
@@ -126,7 +130,8 @@ int striped_forward(const void* x, void* y, const void* Vp, const void* Up, int 
     for (int row0 = 0; row0 < M; row0 += 64) {
         const int rows = (M - row0 < 64) ? (M - row0) : 64;
         const int mp = rows <= 8 ? 8 : (rows <= 16 ? 16 : (rows <= 32 ? 32 : 64));
-        const size_t clear = kCtrlBytes + size_t(3) * mp * (r + 4) * sizeof(float);
+        // up to 8 rows the accumulator words are 64-bit (counted exchange), otherwise fp32
+        const size_t clear = kCtrlBytes + size_t(3) * mp * (r + 4) * (mp == 8 ? sizeof(unsigned long long) : sizeof(float));
         if (!cuda_ok(cudaMemsetAsync(ws, 0, clear, stream))) return DLRB200_ERR_CUDA;
         a.p.x = xb + size_t(row0) * d;
         a.p.y = yb + size_t(row0) * d;
@@ -239,22 +244,22 @@ bool use_cluster_path(int M, int d, int r, int L) {
     if (forced == DLRB200_PATH_STRIPED || forced == DLRB200_PATH_STREAMED || forced == DLRB200_PATH_CLUSTER_SMALL) return false;
     if (!dlr::cluster_supported(d, r, L)) return false;
     if (forced == DLRB200_PATH_CLUSTER) return true;
-    // One 128-row tile on one cluster costs the same for any M <= 128 (1.18 ms at d = 4096, r = 128, L = 143;
-    // 0.89 ms at d = 2048, r = 64, L = 142), while the striped kernel grows with M (0.43 + 0.0155 M ms and
-    // 0.51 + 0.0072 M ms): from about 52 rows on, the padded tile is the faster way.
+    // One 128-row tile on one cluster costs the same for any M <= 128 (1.16 ms at d = 4096, r = 128, L = 143),
+    // while the striped kernel grows with M (about 0.35 + 0.0153 M ms there): from about 52 rows on, the padded
+    // tile is the faster way.  At d = 2048 the striped kernel stays ahead up to 64 rows (0.76 against 0.89 ms).
     if (M > 64) return true;
-    return M >= 52 && d >= 2048;
+    return M >= 52 && d >= 4096;
 }
 
 // Small batches: the cluster kernel (one cluster per pair of rows, exchange in
 // distributed shared memory) or the striped kernel (all SMs on every row,
-// exchange through global memory).  Measured on B200, L about 142: at d = 1024
-// the cluster kernel wins for every M <= 64 (328 us against 337..528 us), at
-// d = 2048 for 2 <= M <= 32 (428 us against 476..650 us), at d = 4096 never
-// (a cluster of 16 SMs cannot pull 2 MB of weights per layer fast enough:
-// 666 us against 420 us at M = 1).  All its clusters must be resident at once
-// to share the weight stream through L2, hence the cap on the grid.
-// DLRB200_FORCE_PATH=1 or 3 overrides the choice.
+// exchange through global memory).  Measured on B200, L about 142 (us): d = 1024:
+// cluster kernel 291 for every M <= 64 against 263 (M = 1), 297 (M = 2..8), 349
+// (M = 16), 490 (M = 64) striped; d = 2048: 386 for M <= 32 against 277 (M = 1),
+// 325 (M = 8), 396 (M = 16) and about 530 (M = 32) striped; d = 4096: 625 against
+// 310 (a cluster of 16 SMs cannot pull 2 MB of weights per layer fast enough).
+// All its clusters must be resident at once to share the weight stream through
+// L2, hence the cap on the grid.  DLRB200_FORCE_PATH=1 or 3 overrides the choice.
 bool use_cluster_small(int M, int d, int r) {
     const int forced = env_int("DLRB200_FORCE_PATH", 0);
     if (forced == DLRB200_PATH_STRIPED || forced == DLRB200_PATH_CLUSTER) return false;
@@ -262,7 +267,7 @@ bool use_cluster_small(int M, int d, int r) {
     if (forced == DLRB200_PATH_CLUSTER_SMALL) return true;
     const int grid = ((M + 1) / 2) * (d / 256);
     if (grid > 128) return false;
-    return d <= 1024 || (d <= 2048 && M >= 2);
+    return (d <= 1024 && M >= 2) || (d <= 2048 && M >= 16);
 }
 
 }  // namespace

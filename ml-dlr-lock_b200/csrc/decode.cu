@@ -18,6 +18,19 @@
 // counter; one thread per CTA polls the counter with acquire loads, with a
 // poll limit.  The launch is cooperative, so all G CTAs are co-resident.
 //
+// Exchange for up to 8 rows (the latency-critical case).  The scheme above costs
+// about three round trips to L2 per layer (reductions performed, counter seen,
+// sums read).  With few rows every accumulator word is instead a 64-bit integer
+// that carries its own arrival count: bits 48-63 count the CTAs that have added,
+// bits 0-47 hold the sum in fixed point (values are first scaled by the row's
+// 1/rms of the layer before, so the format does not depend on the scale of the
+// input).  One red.add.u64 per value and CTA, then every thread polls just the
+// words it needs until their counts are complete: about one and a half round
+// trips, no counter, no fence.  Slots are never cleared: a CTA that adds into a
+// slot again (three layers later) subtracts what it added then, exactly, since
+// integer addition commutes; for the same reason the result does not depend on
+// the order of arrival (the fp32 reductions do).
+//
 // Weight streaming.  Weights do not depend on activations, so each CTA keeps a
 // ring of S layers of its weight slices in flight with TMA tiled loads that
 // complete on mbarriers; the ring is refilled as soon as a layer is consumed.
@@ -36,6 +49,28 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
+
+// ---- counted 64-bit accumulator words (see "Exchange for up to 8 rows") ----
+constexpr double kZScale = 16777216.0;      // 2^24: normalised partial z
+constexpr double kQScale = 65536.0;         // 2^16: normalised partial sums of squares
+constexpr unsigned long long kOneArrival = 1ull << 48;
+
+__device__ __forceinline__ void red_add_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void ld_volatile_2xu64(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
+    unsigned long long a;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+    return a;
+}
+// arrivals recorded in a word (the sum may be negative and borrow from the count: round to the nearest count)
+__device__ __forceinline__ unsigned int word_count(unsigned long long w) { return unsigned((w + (1ull << 47)) >> 48) & 0xffffu; }
+__device__ __forceinline__ long long word_sum(unsigned long long w) {
+    return static_cast<long long>(w - (((w + (1ull << 47)) >> 48) << 48));
+}
 
 template <int R, int DC, int NT>
 struct DecodeCfg {
@@ -92,6 +127,11 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
     const int M = p.M;
     const int col0 = cta * DC;
     const uint32_t ring_s = smem_u32(ring);
+    constexpr bool CNT = NT == 1;                                     // counted 64-bit exchange (up to 8 rows)
+    constexpr int VI = CNT ? (C::MT_V + kWarps - 1) / kWarps : 1;     // V-phase items per warp
+    unsigned long long* zs64 = reinterpret_cast<unsigned long long*>(p.zacc);   // [3][MP][RP]
+    float* pre = reinterpret_cast<float*>(zs64 + 3 * C::MP * C::RP);  // [G][8]: every CTA's sums of squares of the input
+    __shared__ float rs_sh[2][8];                                     // 1/rms per row: of the layer before / of this layer
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) mbar_init(smem_u32(&full[s]), 1);
@@ -140,16 +180,53 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
                 float ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
 #pragma unroll
                 for (int o = GPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                if (cg == 0 && row < M) red_add_f32(zacc + size_t(row) * C::RP + R, ss);
+                if (cg == 0 && row < M) {
+                    if constexpr (CNT) pre[cta * 8 + row] = ss;       // summed in a fixed order below: repeatable
+                    else red_add_f32(zacc + size_t(row) * C::RP + R, ss);
+                }
             }
         }
     }
 
     int err = 0;
     int l = 0;
+    bool nothing_consumed = false;           // gave up before the first layer's weights were waited for
+    if constexpr (CNT) {
+        // ---- the sums of squares of the input, once, through a plain barrier: every later layer scales by the
+        // 1/rms before it
+        __threadfence();
+        __syncthreads();
+        bool failed = false;
+        if (tid == 0) {
+            red_release_add_u32(p.counter, 1u);
+            unsigned int spins = 0;
+            while (ld_acquire_u32(p.counter) < unsigned(G)) {
+                if (++spins > p.spin_limit) { failed = true; break; }
+            }
+        }
+        if (__syncthreads_or(failed)) { err = DLRB200_ERR_TIMEOUT_BARRIER; nothing_consumed = true; }
+        if (tid < C::MP) {
+            float q = 0.f;
+            if (tid < M && !err)
+                for (int c = 0; c < G; ++c) q += __ldcg(pre + c * 8 + tid);
+            rs_sh[0][tid] = rsqrtf(q * p.inv_d + p.eps);
+            // an arrival without a value in the first slot's sum-of-squares words: every word of a slot then
+            // counts the same number of arrivals per use
+            if (tid < M) red_add_u64(zs64 + size_t(tid) * C::RP + R, kOneArrival);
+        }
+        __syncthreads();
+    }
+    long long oldz[3][VI][4];                // what this thread added to a slot the last three times (front = [0])
+    long long oldq[3] = {0, 0, 0};
+#pragma unroll
+    for (int a = 0; a < 3; ++a)
+#pragma unroll
+        for (int b = 0; b < VI; ++b)
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) oldz[a][b][c4] = 0;
     RingPos rpos;
 #pragma unroll 1
-    for (; l < p.L; ++l, rpos.step(uint32_t(S))) {
+    for (; l < p.L && !err; ++l, rpos.step(uint32_t(S))) {
         const int st = int(rpos.st);
         const uint32_t ph = rpos.ph;
         const int slot = l % 3;
@@ -163,6 +240,43 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
         if (__syncthreads_or(!landed)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
 
         // ---- V phase: z_part[r][row] over this stripe, added into the accumulator
+        if constexpr (CNT) {
+            const float* nrm = rs_sh[l & 1];                       // 1/rms of the layer before (of the input at l = 0)
+            unsigned long long* zw = zs64 + size_t(slot) * C::MP * C::RP;
+#pragma unroll
+            for (int vi = 0; vi < VI; ++vi) {
+                const int mt = warp + kWarps * vi;
+                if (mt < C::MT_V) {
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int ks = 0; ks < C::KS_V; ++ks) {
+                        const int arow = 16 * mt + (lane & 7) + ((lane >> 3) & 1) * 8;
+                        const uint32_t off = uint32_t(arow) * (DC * 2) + ks * 32 + (lane >> 4) * 16;
+                        uint32_t a0, a1, a2, a3;
+                        ldmatrix_x4(vbase + swz(off, C::VBITS), a0, a1, a2, a3);
+                        const __nv_bfloat16* bp = hb + g * C::HBS + 16 * ks + 2 * t;
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bp);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(bp + 8);
+                        mma_bf16_16816(c, a0, a1, a2, a3, b0, b1);
+                    }
+                    const int n0 = 2 * t;
+                    const int rr = 16 * mt + g;
+                    // c[0], c[2]: row n0, columns rr, rr+8;  c[1], c[3]: row n0+1
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int row = n0 + (q & 1);
+                        if (row < M) {
+                            const long long e = __double2ll_rn(double(c[q]) * double(nrm[row]) * kZScale);
+                            red_add_u64(zw + size_t(row) * C::RP + rr + 8 * (q >> 1),
+                                        static_cast<unsigned long long>(e - oldz[0][vi][q]) + kOneArrival);
+                            oldz[0][vi][q] = oldz[1][vi][q];
+                            oldz[1][vi][q] = oldz[2][vi][q];
+                            oldz[2][vi][q] = e;
+                        }
+                    }
+                }
+            }
+        } else {
 #pragma unroll 1
         for (int item = warp; item < C::MT_V * NT; item += kWarps) {
             const int mt = item % C::MT_V;
@@ -207,8 +321,61 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
             }
         }
         if (__syncthreads_or(failed)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }  // (C)
+        }
 
         // ---- s = silu(z * rstd) as the 8-wide operand of the U phase
+        if constexpr (CNT) {
+            // every thread polls the words it needs until all G stripes have added to them
+            const unsigned int target = (unsigned(l / 3 + 1) * unsigned(G)) & 0xffffu;
+            const unsigned long long* zw = zs64 + size_t(slot) * C::MP * C::RP;
+            const float* nrm = rs_sh[l & 1];
+            float* rnext = rs_sh[(l + 1) & 1];
+            bool failed = false;
+            // 256 threads of 128 CTAs polling the very lines the reductions go to would slow those down: one
+            // lane per warp watches one word (with a short back-off); the others look only once it is complete,
+            // when theirs almost always are too
+            if (lane == 0) {
+                const unsigned long long* watch = zw + size_t(warp % M) * C::RP + R;
+                unsigned int spins = 0;
+                while (word_count(ld_volatile_u64(watch)) != target) {
+                    if (++spins > p.spin_limit) { failed = true; break; }
+                    if ((spins & 0xffu) == 0xffu && *reinterpret_cast<volatile int*>(p.status) != 0) { failed = true; break; }
+                    __nanosleep(40);
+                }
+            }
+            __syncwarp();
+#pragma unroll 1
+            for (int e = tid; e < C::MP * (R / 4); e += kThreads) {
+                const int row = e / (R / 4);
+                const int k4 = e % (R / 4);
+                uint2 out = make_uint2(0u, 0u);
+                if (row < M) {
+                    unsigned long long w0 = 0, w1 = 0, w2 = 0, w3 = 0, wq = 0;
+                    bool ok = false;
+                    for (unsigned int spins = 0; spins < p.spin_limit; ++spins) {
+                        ld_volatile_2xu64(zw + size_t(row) * C::RP + 4 * k4, w0, w1);
+                        ld_volatile_2xu64(zw + size_t(row) * C::RP + 4 * k4 + 2, w2, w3);
+                        wq = ld_volatile_u64(zw + size_t(row) * C::RP + R);
+                        if (word_count(w0) == target && word_count(w1) == target && word_count(w2) == target &&
+                            word_count(w3) == target && word_count(wq) == target) { ok = true; break; }
+                        if ((spins & 0x3ffu) == 0x3ffu && *reinterpret_cast<volatile int*>(p.status) != 0) break;
+                    }
+                    if (!ok) failed = true;
+                    const float rprev = nrm[row];
+                    float rstd = rprev;                         // layer 0: the input's 1/rms, known already
+                    if (l > 0) {
+                        const float q = float(double(word_sum(wq)) * (1.0 / kQScale)) / (rprev * rprev);
+                        rstd = rsqrtf(q * p.inv_d + p.eps);
+                    }
+                    if (k4 == 0) rnext[row] = rstd;
+                    const float sc = rstd / rprev * float(1.0 / kZScale);
+                    out.x = pack_bf16x2(silu_f(float(word_sum(w0)) * sc), silu_f(float(word_sum(w1)) * sc));
+                    out.y = pack_bf16x2(silu_f(float(word_sum(w2)) * sc), silu_f(float(word_sum(w3)) * sc));
+                }
+                *reinterpret_cast<uint2*>(sb + row * C::SS + 4 * k4) = out;
+            }
+            if (__syncthreads_or(failed)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }  // (D)
+        } else {
 #pragma unroll 1
         for (int e = tid; e < C::MP * (R / 4); e += kThreads) {
             const int row = e / (R / 4);
@@ -235,6 +402,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
             }
         }
         __syncthreads();  // (D)
+        }
 
         // ---- U phase: dh[stripe col][row], split over k when there are few tiles
 #pragma unroll 1
@@ -290,7 +458,19 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
                     float ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
 #pragma unroll
                     for (int o = GPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                    if (cg == 0 && row < M) red_add_f32(znext + size_t(row) * C::RP + R, ss);
+                    if (cg == 0 && row < M) {
+                        if constexpr (CNT) {
+                            const float rcur = rs_sh[(l + 1) & 1][row];          // this layer's 1/rms
+                            const long long e = __double2ll_rn(double(ss) * double(rcur) * double(rcur) * kQScale);
+                            red_add_u64(zs64 + (size_t((l + 1) % 3) * C::MP + row) * C::RP + R,
+                                        static_cast<unsigned long long>(e - oldq[0]) + kOneArrival);
+                            oldq[0] = oldq[1];
+                            oldq[1] = oldq[2];
+                            oldq[2] = e;
+                        } else {
+                            red_add_f32(znext + size_t(row) * C::RP + R, ss);
+                        }
+                    }
                 } else if (row < M) {
                     *reinterpret_cast<uint2*>(p.y + size_t(row) * p.d + col0 + 4 * cg) = packed;
                 }
@@ -304,7 +484,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
         if (tid == 0) {
             atomicCAS(p.status, 0, err | (l << 8));
             const int hi = (l + S < p.L) ? l + S : p.L;
-            const int lo = (err == DLRB200_ERR_TIMEOUT_COPY) ? l : l + 1;
+            const int lo = (err == DLRB200_ERR_TIMEOUT_COPY || nothing_consumed) ? l : l + 1;
             for (int j = lo; j < hi; ++j) mbar_wait(smem_u32(&full[j % S]), (j / S) & 1, kDrainPolls);
         }
         __syncthreads();

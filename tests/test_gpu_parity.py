@@ -94,7 +94,8 @@ def test_rows_are_independent_and_input_is_untouched(D):
     torch.cuda.synchronize()
     D.ops.check_status()
     assert torch.equal(xd, keep)
-    assert O.rel_l2(y_one.cpu(), y_all[5:6].cpu()) <= 1e-3
+    # one row and 24 rows may run on different kernels (bf16 or fp32 operands for h): same math, not the same bits
+    assert O.rel_l2(y_one.cpu(), y_all[5:6].cpu()) <= 5e-3
     assert O.rel_l2(y_perm.cpu(), y_all[perm].cpu()) <= 1e-3
 
 
@@ -182,7 +183,7 @@ def test_abi_argument_errors(D):
     assert lib.dlrb200_forward(*args(x=vp(y))) == 1             # aliasing
     torch.cuda.synchronize()
     plan = D.ops.query(4, 4096, 128, 143)
-    assert plan.path in (1, 3) and plan.stripe_cols * plan.cluster in (4096, 32)
+    assert plan.path == 1 and plan.stripe_cols == 64 and plan.grid == 64
 
 
 def test_host_buffer_entry_point(D):
@@ -385,3 +386,29 @@ def test_forward_can_be_captured_in_a_cuda_graph(D):
         torch.cuda.synchronize()
         D.ops.check_status()
         assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("d,r,L,M", [(4096, 128, 143, 1), (4096, 128, 21, 8), (5120, 256, 9, 3), (2048, 64, 12, 1),
+                                     (256, 16, 7, 5)])
+def test_small_batch_exchange_is_exact_and_repeatable(D, d, r, L, M, monkeypatch):
+    # up to 8 rows the striped kernel sums the partial z in 64-bit fixed point with an arrival count in
+    # every word: the result must not depend on the order in which the stripes arrive (two runs give the
+    # same bits), must not depend on the scale of the input (partials are normalised by the running
+    # 1/rms), and must match the fp32 oracle
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "1")
+    dev = torch.device("cuda:0")
+    p, x = O.seeded_case(d, r, L, M, seed=d + L + M, alpha=0.05 if L > 50 else 1.0, gain_jitter=0.1)
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    xd = x.to(dev)
+    y1 = D.ops.forward_folded(xd, Vf, Uf, p.eps)
+    y2 = D.ops.forward_folded(xd, Vf, Uf, p.eps)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert torch.equal(y1, y2)
+    assert O.rel_l2(y1.cpu(), O.forward_fp32(x, p)) <= 5e-3
+    for scale in (1e-3, 1e3):               # RMS-normalised layers: y(c x) = c y(x) up to eps and rounding
+        xs = (x.float() * scale).to(torch.bfloat16)
+        ys = D.ops.forward_folded(xs.to(dev), Vf, Uf, p.eps)
+        torch.cuda.synchronize()
+        D.ops.check_status()
+        assert O.rel_l2(ys.cpu().float(), O.forward_fp32(xs, p).float()) <= 1e-2
