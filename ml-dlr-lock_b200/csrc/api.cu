@@ -130,8 +130,8 @@ int striped_forward(const void* x, void* y, const void* Vp, const void* Up, int 
     for (int row0 = 0; row0 < M; row0 += 64) {
         const int rows = (M - row0 < 64) ? (M - row0) : 64;
         const int mp = rows <= 8 ? 8 : (rows <= 16 ? 16 : (rows <= 32 ? 32 : 64));
-        // up to 8 rows the accumulator words are 64-bit (counted exchange), otherwise fp32
-        const size_t clear = kCtrlBytes + size_t(3) * mp * (r + 4) * (mp == 8 ? sizeof(unsigned long long) : sizeof(float));
+        // up to 16 rows the accumulator words are 64-bit (counted exchange), otherwise fp32
+        const size_t clear = kCtrlBytes + size_t(3) * mp * (r + 4) * (mp <= 16 ? sizeof(unsigned long long) : sizeof(float));
         if (!cuda_ok(cudaMemsetAsync(ws, 0, clear, stream))) return DLRB200_ERR_CUDA;
         a.p.x = xb + size_t(row0) * d;
         a.p.y = yb + size_t(row0) * d;
@@ -256,7 +256,7 @@ bool use_cluster_path(int M, int d, int r, int L) {
 // exchange through global memory).  Measured on B200, L about 142 (us): d = 1024:
 // cluster kernel 291 for every M <= 64 against 263 (M = 1), 297 (M = 2..8), 349
 // (M = 16), 490 (M = 64) striped; d = 2048: 386 for M <= 32 against 277 (M = 1),
-// 325 (M = 8), 396 (M = 16) and about 530 (M = 32) striped; d = 4096: 625 against
+// 325 (M = 8), 344 (M = 16) and about 530 (M = 32) striped; d = 4096: 625 against
 // 310 (a cluster of 16 SMs cannot pull 2 MB of weights per layer fast enough).
 // All its clusters must be resident at once to share the weight stream through
 // L2, hence the cap on the grid.  DLRB200_FORCE_PATH=1 or 3 overrides the choice.
@@ -267,7 +267,7 @@ bool use_cluster_small(int M, int d, int r) {
     if (forced == DLRB200_PATH_CLUSTER_SMALL) return true;
     const int grid = ((M + 1) / 2) * (d / 256);
     if (grid > 128) return false;
-    return (d <= 1024 && M >= 2) || (d <= 2048 && M >= 16);
+    return (d <= 1024 && M >= 2) || (d <= 2048 && M > 16);
 }
 
 }  // namespace

@@ -18,7 +18,7 @@
 // counter; one thread per CTA polls the counter with acquire loads, with a
 // poll limit.  The launch is cooperative, so all G CTAs are co-resident.
 //
-// Exchange for up to 8 rows (the latency-critical case).  The scheme above costs
+// Exchange for up to 16 rows (the latency-critical case).  The scheme above costs
 // about three round trips to L2 per layer (reductions performed, counter seen,
 // sums read).  With few rows every accumulator word is instead a 64-bit integer
 // that carries its own arrival count: bits 48-63 count the CTAs that have added,
@@ -127,11 +127,11 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
     const int M = p.M;
     const int col0 = cta * DC;
     const uint32_t ring_s = smem_u32(ring);
-    constexpr bool CNT = NT == 1;                                     // counted 64-bit exchange (up to 8 rows)
-    constexpr int VI = CNT ? (C::MT_V + kWarps - 1) / kWarps : 1;     // V-phase items per warp
+    constexpr bool CNT = NT <= 2;                                     // counted 64-bit exchange (up to 16 rows)
+    constexpr int VI = CNT ? (C::MT_V * NT + kWarps - 1) / kWarps : 1;   // V-phase items per warp
     unsigned long long* zs64 = reinterpret_cast<unsigned long long*>(p.zacc);   // [3][MP][RP]
-    float* pre = reinterpret_cast<float*>(zs64 + 3 * C::MP * C::RP);  // [G][8]: every CTA's sums of squares of the input
-    __shared__ float rs_sh[2][8];                                     // 1/rms per row: of the layer before / of this layer
+    float* pre = reinterpret_cast<float*>(zs64 + 3 * C::MP * C::RP);  // [G][16]: every CTA's sums of squares of the input
+    __shared__ float rs_sh[2][16];                                     // 1/rms per row: of the layer before / of this layer
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) mbar_init(smem_u32(&full[s]), 1);
@@ -181,7 +181,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
 #pragma unroll
                 for (int o = GPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 if (cg == 0 && row < M) {
-                    if constexpr (CNT) pre[cta * 8 + row] = ss;       // summed in a fixed order below: repeatable
+                    if constexpr (CNT) pre[cta * 16 + row] = ss;       // summed in a fixed order below: repeatable
                     else red_add_f32(zacc + size_t(row) * C::RP + R, ss);
                 }
             }
@@ -208,7 +208,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
         if (tid < C::MP) {
             float q = 0.f;
             if (tid < M && !err)
-                for (int c = 0; c < G; ++c) q += __ldcg(pre + c * 8 + tid);
+                for (int c = 0; c < G; ++c) q += __ldcg(pre + c * 16 + tid);
             rs_sh[0][tid] = rsqrtf(q * p.inv_d + p.eps);
             // an arrival without a value in the first slot's sum-of-squares words: every word of a slot then
             // counts the same number of arrivals per use
@@ -245,8 +245,10 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
             unsigned long long* zw = zs64 + size_t(slot) * C::MP * C::RP;
 #pragma unroll
             for (int vi = 0; vi < VI; ++vi) {
-                const int mt = warp + kWarps * vi;
-                if (mt < C::MT_V) {
+                const int item = warp + kWarps * vi;
+                const int mt = item % C::MT_V;
+                const int nt = item / C::MT_V;
+                if (item < C::MT_V * NT) {
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                     for (int ks = 0; ks < C::KS_V; ++ks) {
@@ -254,12 +256,12 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
                         const uint32_t off = uint32_t(arow) * (DC * 2) + ks * 32 + (lane >> 4) * 16;
                         uint32_t a0, a1, a2, a3;
                         ldmatrix_x4(vbase + swz(off, C::VBITS), a0, a1, a2, a3);
-                        const __nv_bfloat16* bp = hb + g * C::HBS + 16 * ks + 2 * t;
+                        const __nv_bfloat16* bp = hb + (8 * nt + g) * C::HBS + 16 * ks + 2 * t;
                         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bp);
                         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(bp + 8);
                         mma_bf16_16816(c, a0, a1, a2, a3, b0, b1);
                     }
-                    const int n0 = 2 * t;
+                    const int n0 = 8 * nt + 2 * t;
                     const int rr = 16 * mt + g;
                     // c[0], c[2]: row n0, columns rr, rr+8;  c[1], c[3]: row n0+1
 #pragma unroll

@@ -389,9 +389,9 @@ def test_forward_can_be_captured_in_a_cuda_graph(D):
 
 
 @pytest.mark.parametrize("d,r,L,M", [(4096, 128, 143, 1), (4096, 128, 21, 8), (5120, 256, 9, 3), (2048, 64, 12, 1),
-                                     (256, 16, 7, 5)])
+                                     (256, 16, 7, 5), (4096, 128, 17, 16), (5120, 256, 5, 12), (1024, 32, 9, 11)])
 def test_small_batch_exchange_is_exact_and_repeatable(D, d, r, L, M, monkeypatch):
-    # up to 8 rows the striped kernel sums the partial z in 64-bit fixed point with an arrival count in
+    # up to 16 rows the striped kernel sums the partial z in 64-bit fixed point with an arrival count in
     # every word: the result must not depend on the order in which the stripes arrive (two runs give the
     # same bits), must not depend on the scale of the input (partials are normalised by the running
     # 1/rms), and must match the fp32 oracle
