@@ -155,7 +155,7 @@ DLRB200_API int dlrb200_transpose_stack(const void* src, void* dst, int L, int r
  *   on the stream at the start of the call, and two calls that overlap on the
  *   GPU (different streams, no dependency) race - serialise them. */
 #define DLRB200_STATIC_MAX_ROWS 64
-#define DLRB200_STATIC_SCRATCH_BYTES 200704
+#define DLRB200_STATIC_SCRATCH_BYTES 221184
 DLRB200_API int dlrb200_forward_static(const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r,
                                        int L, float eps, int* status_dev, void* stream);
 

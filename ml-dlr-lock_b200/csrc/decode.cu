@@ -50,7 +50,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 
-// ---- counted 64-bit accumulator words (see "Exchange for up to 8 rows") ----
+// ---- counted 64-bit accumulator words (see "Exchange for up to 16 rows") ----
 constexpr double kZScale = 16777216.0;      // 2^24: normalised partial z
 constexpr double kQScale = 65536.0;         // 2^16: normalised partial sums of squares
 constexpr unsigned long long kOneArrival = 1ull << 48;
@@ -127,11 +127,13 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
     const int M = p.M;
     const int col0 = cta * DC;
     const uint32_t ring_s = smem_u32(ring);
-    constexpr bool CNT = NT <= 2;                                     // counted 64-bit exchange (up to 16 rows)
+    // counted 64-bit exchange, up to 16 rows: beyond that a thread updates several rows per layer and the
+    // bookkeeping of what it added (oldz, oldq) no longer fits
+    constexpr bool CNT = NT <= 2;
     constexpr int VI = CNT ? (C::MT_V * NT + kWarps - 1) / kWarps : 1;   // V-phase items per warp
     unsigned long long* zs64 = reinterpret_cast<unsigned long long*>(p.zacc);   // [3][MP][RP]
-    float* pre = reinterpret_cast<float*>(zs64 + 3 * C::MP * C::RP);  // [G][16]: every CTA's sums of squares of the input
-    __shared__ float rs_sh[2][16];                                     // 1/rms per row: of the layer before / of this layer
+    float* pre = reinterpret_cast<float*>(zs64 + 3 * C::MP * C::RP);  // [G][32]: every CTA's sums of squares of the input
+    __shared__ float rs_sh[2][32];                                     // 1/rms per row: of the layer before / of this layer
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) mbar_init(smem_u32(&full[s]), 1);
@@ -181,7 +183,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
 #pragma unroll
                 for (int o = GPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 if (cg == 0 && row < M) {
-                    if constexpr (CNT) pre[cta * 16 + row] = ss;       // summed in a fixed order below: repeatable
+                    if constexpr (CNT) pre[cta * 32 + row] = ss;       // summed in a fixed order below: repeatable
                     else red_add_f32(zacc + size_t(row) * C::RP + R, ss);
                 }
             }
@@ -208,7 +210,7 @@ dlr_decode_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant
         if (tid < C::MP) {
             float q = 0.f;
             if (tid < M && !err)
-                for (int c = 0; c < G; ++c) q += __ldcg(pre + c * 16 + tid);
+                for (int c = 0; c < G; ++c) q += __ldcg(pre + c * 32 + tid);
             rs_sh[0][tid] = rsqrtf(q * p.inv_d + p.eps);
             // an arrival without a value in the first slot's sum-of-squares words: every word of a slot then
             // counts the same number of arrivals per use
@@ -545,7 +547,9 @@ int launch_dc(const DecodeLaunch& a) {
 
 }  // namespace
 
-size_t decode_zacc_floats(int r) { return size_t(3) * 64 * (r + 4); }
+// three slots of 64 rows x (r + 4) fp32 words (or 32 rows of 64-bit words), then every CTA's sums of squares of
+// the input: up to 160 CTAs (one per SM) x 32 rows
+size_t decode_zacc_floats(int r) { return size_t(3) * 64 * (r + 4) + size_t(160) * 32; }
 
 bool decode_box_dims(int r, int dc, int* v_box_cols, int* v_box_rows, int* u_box_cols, int* u_box_rows,
                      int* v_swizzle_bytes, int* u_swizzle_bytes) {
