@@ -20,6 +20,7 @@ from .model import (  # noqa: F401
     set_fast_path,
     write_config,
 )
-from . import ops, registry, sharding  # noqa: F401
+from . import ops, packed, registry, sharding  # noqa: F401
+from .packed import PackedNet, load_packed_weights, pack_state_dict  # noqa: F401
 
 __version__ = "0.1.0"

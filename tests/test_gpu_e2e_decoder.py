@@ -63,3 +63,34 @@ def test_locked_decoder_prefill_and_decode_logits():
             D.ops.check_status()
             assert _rel(of.logits, oe.logits) <= 3e-2
             tok = oe.logits[:, -1:].argmax(-1)
+
+
+def test_checkpoint_to_packed_weights(tmp_path):
+    # layerNN.pt files written by save_dlrnet_weights, read straight into folded device stacks: the same
+    # bits as the module computes from the same parameters, with and without the packed cache
+    import os
+
+    import dlr_lock_b200 as D
+    from transformers import AutoConfig
+
+    dev = "cuda:0"
+    torch.manual_seed(1)
+    cfg = AutoConfig.for_model("qwen3", vocab_size=128, hidden_size=512, intermediate_size=1536, num_hidden_layers=2,
+                               num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=64,
+                               tie_word_embeddings=True)
+    model = D.locked_model_from_config(cfg, rank=64, device=dev, alpha_init=0.3).eval()
+    ckpt = str(tmp_path / "ckpt")
+    assert D.save_dlrnet_weights(model, ckpt) == 2
+    x = torch.randn(70, 512, device=dev).to(torch.bfloat16)
+    with torch.no_grad():
+        want = [layer.mlp.dlrnet(x) for layer in model.model.layers]
+    nets = D.load_packed_weights(ckpt, dev, write_cache=True)
+    assert len(nets) == 2 and nets[0].d == 512 and nets[0].r == 64 and nets[0].depth == model.model.layers[0].mlp.dlrnet.depth
+    assert sorted(os.listdir(os.path.join(ckpt, "packed_b200"))) == ["layer00.pt", "layer01.pt"]
+    again = D.load_packed_weights(ckpt, dev)                       # served from the packed cache
+    torch.cuda.synchronize()
+    for w, a, b in zip(want, nets, again):
+        assert torch.equal(a(x), w) and torch.equal(b(x), w)
+    D.ops.check_status()
+    with pytest.raises(ValueError):
+        D.pack_state_dict({"Vs.0": torch.zeros(4, 8)}, dev)
