@@ -345,6 +345,7 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
             // ---- add up the CS partials, normalise, SiLU
             if (ok && tid < C::ZF) {
                 float z = 0.f, q = 0.f;
+#pragma unroll 4
                 for (int src = 0; src < CS; ++src) {
                     z += recvb[src * C::SRC_FLOATS + tid];
                     q += recvb[src * C::SRC_FLOATS + C::ZF + (tid & 1)];
@@ -357,7 +358,9 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
             q1c = DC_CLK(); pc[3] += q1c - q0c; q0c = q1c;
 
             // ---- U phase: column `tid` of the stripe: dot of its U' row with s, both token rows
-            float d0 = 0.f, d1 = 0.f;
+            // four partial sums per token row: the products of a chunk are independent, one accumulator each would
+            // make the phase a chain of dependent FMAs
+            float d0 = 0.f, d1 = 0.f, e0 = 0.f, e1 = 0.f, f0 = 0.f, f1 = 0.f, g0 = 0.f, g1 = 0.f;
             ok = wait_cta(smem_u32(&bars->full[rp.st]), (lead >> rp.st) & 1u) && ok;            // all U' tiles of the layer
             lead ^= 1u << rp.st;
 #pragma unroll 1
@@ -378,20 +381,20 @@ dlr_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_
                         const float w0 = bf16lo_to_f(wv.x), w1 = bf16hi_to_f(wv.x), w2 = bf16lo_to_f(wv.y), w3 = bf16hi_to_f(wv.y);
                         const float w4 = bf16lo_to_f(wv.z), w5 = bf16hi_to_f(wv.z), w6 = bf16lo_to_f(wv.w), w7 = bf16hi_to_f(wv.w);
                         d0 = fmaf(w0, a.x, d0); d1 = fmaf(w0, a.y, d1);
-                        d0 = fmaf(w1, a.z, d0); d1 = fmaf(w1, a.w, d1);
-                        d0 = fmaf(w2, b.x, d0); d1 = fmaf(w2, b.y, d1);
-                        d0 = fmaf(w3, b.z, d0); d1 = fmaf(w3, b.w, d1);
+                        e0 = fmaf(w1, a.z, e0); e1 = fmaf(w1, a.w, e1);
+                        f0 = fmaf(w2, b.x, f0); f1 = fmaf(w2, b.y, f1);
+                        g0 = fmaf(w3, b.z, g0); g1 = fmaf(w3, b.w, g1);
                         d0 = fmaf(w4, c.x, d0); d1 = fmaf(w4, c.y, d1);
-                        d0 = fmaf(w5, c.z, d0); d1 = fmaf(w5, c.w, d1);
-                        d0 = fmaf(w6, e.x, d0); d1 = fmaf(w6, e.y, d1);
-                        d0 = fmaf(w7, e.z, d0); d1 = fmaf(w7, e.w, d1);
+                        e0 = fmaf(w5, c.z, e0); e1 = fmaf(w5, c.w, e1);
+                        f0 = fmaf(w6, e.x, f0); f1 = fmaf(w6, e.y, f1);
+                        g0 = fmaf(w7, e.z, g0); g1 = fmaf(w7, e.w, g1);
                     }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars->empty[st]));
             }
-            h0 += d0;
-            h1 += d1;
+            h0 += (d0 + e0) + (f0 + g0);
+            h1 += (d1 + e1) + (f1 + g1);
             publish_h();
             if (!ok) *abort_flag = 1;
             bar_compute();
