@@ -183,6 +183,10 @@ def min_latency_us(fn, iters=200, warmup=20):
 # --------------------------------------------------------------------------- #
 def cpu_forward_sampler(d, r, L, seed, rows):
     from oracle import dlrnet_oracle as O
+    # torchrun pins OMP_NUM_THREADS to 1 for every rank; the CPU arm runs on one rank only and may use the host
+    n = os.cpu_count() or 1
+    if torch.get_num_threads() < n:
+        torch.set_num_threads(min(n, 64))
     p, x = O.seeded_case(d, r, L, rows, seed, alpha=0.01)
     return lambda: O.forward_eager(x, p)
 
