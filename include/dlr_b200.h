@@ -107,7 +107,13 @@ DLRB200_API int dlrb200_query(int M, int d, int r, int L, dlrb200_plan* plan);
  *   status_dev  one int in device memory, zero before the first call.  It is
  *               written only if a bounded device-side wait gives up:
  *               (layer << 8) | DLRB200_ERR_TIMEOUT_*; the output is then
- *               undefined.  The caller reads it after synchronising.
+ *               undefined.  The caller reads it after synchronising (or
+ *               mirrors it to host memory with dlrb200_status_to_host).
+ *               A non-zero word is also an abort signal: every kernel of the
+ *               library that is given this word, on any stream and through
+ *               any entry point, makes its waits give up while it is set, so
+ *               later calls return undefined output too.  After reading a
+ *               non-zero value the caller must set the word back to 0.
  *   stream      a cudaStream_t (NULL = legacy default stream).
  * Supported: d a multiple of 16, r in {16, 32, 64, 128, 256}, M >= 1, L >= 1
  * (M = 0 returns DLRB200_OK and does nothing). */
@@ -121,6 +127,15 @@ DLRB200_API int dlrb200_forward(const void* x, void* y, const void* Vp, const vo
 DLRB200_API int dlrb200_forward_host(const void* x_host, void* y_host, void* x_dev, void* y_dev, const void* Vp,
                          const void* Up, int M, int d, int r, int L, float eps, void* workspace,
                          size_t workspace_bytes, int* status_dev, void* stream);
+
+/* Queue a 4-byte copy of the device status word to `status_host` (pinned host
+ * memory) on `stream`, behind the forwards already queued there.  A serving
+ * loop can then notice a device-side timeout by reading host memory at its next
+ * call, without synchronising the stream.  Stands in for the TORCH_CHECK errors
+ * of the reference's entry points (kernels/kernels/cuda/cooperative.cu:602-607),
+ * which have no device-side failure mode to report because their waits are
+ * unbounded. */
+DLRB200_API int dlrb200_status_to_host(const int* status_dev, int* status_host, void* stream);
 
 /* Fold the per-layer gain into V and the ReZero scalar into U and stack the
  * result in the layouts dlrb200_forward takes.

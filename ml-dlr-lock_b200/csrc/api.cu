@@ -83,10 +83,13 @@ bool supported_rank(int r) { return r == 16 || r == 32 || r == 64 || r == 128 ||
 // (32), 258 / 320 (16).  All CTAs must be co-resident (one per SM).
 int pick_stripe_cols(int d, int num_sms) {
     const int forced = env_int("DLRB200_STRIPE_COLS", 0);
-    if (forced == 16 || forced == 32 || forced == 64) return (d % forced == 0) ? forced : 0;
+    // a forced width obeys the same limit: one CTA per SM, and the per-CTA words of the workspace are sized for
+    // at most 160 CTAs
+    if (forced == 16 || forced == 32 || forced == 64)
+        return (d % forced == 0 && d / forced <= num_sms && d / forced <= 160) ? forced : 0;
     const int want = d >= 2048 ? 64 : 32;
     for (int dc : {64, 32, 16})
-        if (dc <= want && d % dc == 0 && d / dc <= num_sms) return dc;
+        if (dc <= want && d % dc == 0 && d / dc <= num_sms && d / dc <= 160) return dc;
     return 0;
 }
 
@@ -204,10 +207,12 @@ int check_shape(int M, int d, int r, int L) {
 // Shapes the cluster kernel does not cover (d > 4096, d not a multiple of 512, r > d / 32) always stream:
 // 3.7 ms against 27.6 ms on the striped kernel at d = 8192, M = 4096.
 struct RouteEntry {
-    int M, d, r, L, sms, streamed;
+    int tiles, d, r, L, sms, streamed;     // both plans depend on M only through the number of 128-row tiles
 };
-RouteEntry g_route[32];
-int g_route_n = 0;
+constexpr int kRouteSlots = 32;
+RouteEntry g_route[kRouteSlots];
+int g_route_n = 0;          // entries in use
+int g_route_next = 0;       // slot the next new shape goes to (oldest first once the table is full)
 std::mutex g_route_mutex;
 
 bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
@@ -216,11 +221,12 @@ bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
     if (forced == DLRB200_PATH_STREAMED) return true;
     if (forced != 0) return false;
     if (!dlr::cluster_supported(d, r, L)) return true;
+    const int tiles = (M + 127) / 128;
     {   // the two plans below ask the driver for occupancy: remember the answer per shape
         std::lock_guard<std::mutex> lock(g_route_mutex);
         for (int i = 0; i < g_route_n; ++i) {
             const RouteEntry& e = g_route[i];
-            if (e.M == M && e.d == d && e.r == r && e.L == L && e.sms == di.num_sms) return e.streamed != 0;
+            if (e.tiles == tiles && e.d == d && e.r == r && e.L == L && e.sms == di.num_sms) return e.streamed != 0;
         }
     }
     dlrb200_plan pc, ps;
@@ -234,8 +240,9 @@ bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
     if (ps.cluster == 1 && ps.grid > 100 && 4.0 * L * d * r > 100e6) t_stream *= 1.3;
     const bool streamed = t_stream < 0.97 * t_cluster;
     std::lock_guard<std::mutex> lock(g_route_mutex);
-    g_route[g_route_n % 32] = RouteEntry{M, d, r, L, di.num_sms, streamed ? 1 : 0};
-    if (g_route_n < 32) ++g_route_n;
+    g_route[g_route_next] = RouteEntry{tiles, d, r, L, di.num_sms, streamed ? 1 : 0};
+    g_route_next = (g_route_next + 1) % kRouteSlots;
+    if (g_route_n < kRouteSlots) ++g_route_n;
     return streamed;
 }
 
@@ -411,6 +418,14 @@ int dlrb200_forward_host(const void* x_host, void* y_host, void* x_dev, void* y_
     if (rc != DLRB200_OK) return rc;
     if (!cuda_ok(cudaMemcpyAsync(y_host, y_dev, bytes, cudaMemcpyDeviceToHost, st))) return DLRB200_ERR_CUDA;
     return DLRB200_OK;
+}
+
+int dlrb200_status_to_host(const int* status_dev, int* status_host, void* stream) {
+    if (!status_dev || !status_host) return DLRB200_ERR_INVALID_ARG;
+    return cuda_ok(cudaMemcpyAsync(status_host, status_dev, sizeof(int), cudaMemcpyDeviceToHost,
+                                   static_cast<cudaStream_t>(stream)))
+               ? DLRB200_OK
+               : DLRB200_ERR_CUDA;
 }
 
 int dlrb200_fold_weights(const void* V, const void* U, const void* gain, const float* alpha, void* Vp,

@@ -38,6 +38,7 @@ SIGNATURES = {
     "dlrb200_forward_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp, _sz, _vp, _vp]),
     "dlrb200_fold_weights": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dlrb200_transpose_stack": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "dlrb200_status_to_host": (_i, [_vp, _vp, _vp]),
     "dlrb200_forward_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp, _vp]),
 }
 

@@ -89,12 +89,18 @@ class DLRNet(nn.Module):
 
     # ---- derived folded weights ----------------------------------------------
     def _cache_key(self):
-        ps = (self.Vs[0], self.Us[0], self.rms_w[0], self.alphas[0],
-              self.Vs[-1], self.Us[-1], self.rms_w[-1], self.alphas[-1])
-        return tuple((p.data_ptr(), p._version) for p in ps)
+        # every parameter of every layer: storage address and in-place version counter.  A write through
+        # ``p.data`` (``p.data.copy_(...)``) bumps neither: call ``invalidate()`` after such an edit.
+        key = []
+        for plist in (self.Vs, self.Us, self.rms_w, self.alphas):
+            for p in plist:
+                key.append(p.data_ptr())
+                key.append(p._version)
+        return tuple(key)
 
     def invalidate(self):
-        """Drop the folded weights; they are rebuilt on the next fast forward."""
+        """Drop the folded weights; they are rebuilt on the next fast forward.  Needed after writes
+        that bypass autograd's version counter (``p.data.copy_``, ``p.data[...] = ``)."""
         self._folded = None
 
     def folded_weights(self):
@@ -128,7 +134,10 @@ class DLRNet(nn.Module):
             return False
         if self.Vs[0].dtype != torch.bfloat16:
             return False
-        if torch.is_grad_enabled() and (x.requires_grad or self.Vs[0].requires_grad and self.training):
+        # the library returns a tensor without an autograd graph: whenever a gradient could be asked for,
+        # towards the input or towards any parameter, in train or eval mode, the torch loop runs
+        # (the reference's forward always builds the graph, dlr_lock/model.py:88-101)
+        if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
             return False
         return True
 

@@ -22,8 +22,23 @@ from . import _lib
 
 EPS = 1e-6
 
-_workspaces: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
+class _Scratch:
+    """Per (device, stream): workspace, device status word and its pinned host mirror."""
+
+    __slots__ = ("ws", "status", "status_host", "retired")
+
+    def __init__(self, device: torch.device, nbytes: int):
+        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        # workspaces that were outgrown: a CUDA graph captured earlier has their address in its nodes, so
+        # they stay allocated for the life of the process (they are small: at most a few tens of MB)
+        self.retired = []
+
+
+_workspaces: Dict[Tuple[int, int], _Scratch] = {}
 _derived: Dict[Tuple, Tuple[torch.Tensor, ...]] = {}
+_MIN_WORKSPACE = 1 << 20
 
 
 def _ptr(t: torch.Tensor) -> ctypes.c_void_p:
@@ -34,31 +49,55 @@ def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
-def _workspace(device: torch.device, nbytes: int):
+def _raise_status(ent: _Scratch, word: int):
+    ent.status_host.zero_()
+    ent.status.zero_()          # a non-zero word makes later calls give up early: clear it before reporting
+    raise _lib.DlrB200Error(word & 0xff, f"device status: {_lib.strerror(word & 0xff)} at layer {word >> 8}")
+
+
+def _workspace(device: torch.device, nbytes: int) -> _Scratch:
     """Scratch + status word for the current (device, stream); grown on demand.
 
-    One workspace per stream, because calls that share one must not overlap.
+    One workspace per stream, because calls that share one must not overlap.  A workspace that is outgrown
+    is kept, not freed: a CUDA graph captured while it was current still clears and uses that memory on
+    every replay.  Also the lazy error check: the status word of the calls before, mirrored to pinned host
+    memory by a copy on the stream after every forward, is looked at here without synchronising.
     """
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
     ent = _workspaces.get(key)
-    if ent is None or ent[0].numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        status = ent[1] if ent is not None else torch.zeros(1, dtype=torch.int32, device=device)
-        ent = (ws, status)
+    if ent is None:
+        ent = _Scratch(device, max(nbytes, _MIN_WORKSPACE))
         _workspaces[key] = ent
+    else:
+        word = int(ent.status_host[0])
+        if word != 0 and not torch.cuda.is_current_stream_capturing():
+            _raise_status(ent, word)
+        if ent.ws.numel() < nbytes:
+            ent.retired.append(ent.ws)
+            ent.ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
     return ent
 
 
+def _mirror_status(lib, ent: _Scratch, device: torch.device) -> None:
+    """Queue the 4-byte copy of the status word to its pinned host mirror behind the forward."""
+    rc = lib.dlrb200_status_to_host(_ptr(ent.status), ctypes.c_void_p(ent.status_host.data_ptr()),
+                                    _stream_ptr(device))
+    _lib.check(rc, "dlrb200_status_to_host")
+
+
 def check_status(device=None) -> None:
-    """Synchronise and raise if a bounded device-side wait gave up on `device`."""
-    for (dev, _), (_, status) in list(_workspaces.items()):
+    """Synchronise and raise if a bounded device-side wait gave up on `device`.
+
+    Without this call a timeout still surfaces, one call late: every forward mirrors the status word to
+    pinned host memory on its stream, and the next forward on that stream looks at the mirror first.
+    """
+    for (dev, _), ent in list(_workspaces.items()):
         if device is not None and torch.device(device).index not in (None, dev):
             continue
-        word = int(status.item())
+        word = int(ent.status.item())
         if word != 0:
-            status.zero_()
-            raise _lib.DlrB200Error(word & 0xff, f"device status: {_lib.strerror(word & 0xff)} at layer {word >> 8}")
+            _raise_status(ent, word)
 
 
 def _check_inputs(x, Vp, Up):
@@ -83,7 +122,8 @@ def forward_folded(x: torch.Tensor, Vp: torch.Tensor, Up: torch.Tensor, eps: flo
     """y = DLRNet(x) on folded weights; x is (..., d) bf16 on CUDA, y is a new tensor.
 
     Asynchronous on the current stream.  A device-side timeout is reported by
-    ``check_status`` (called by the caller after synchronising), not here.
+    ``check_status`` (which synchronises) or, without a synchronisation, by the
+    next forward on the same stream that runs after the failed one has finished.
     """
     L, r, d = _check_inputs(x, Vp, Up)
     lib = _lib.load()
@@ -98,10 +138,11 @@ def forward_folded(x: torch.Tensor, Vp: torch.Tensor, Up: torch.Tensor, eps: flo
         need = lib.dlrb200_workspace_bytes(M, d, r, L)
         if need == 0:
             _lib.check(2, f"dlrb200_forward(M={M}, d={d}, r={r}, L={L})")
-        ws, status = _workspace(x.device, need)
+        ent = _workspace(x.device, need)
         rc = lib.dlrb200_forward(_ptr(x2), _ptr(y2), _ptr(Vp), _ptr(Up), M, d, r, L, float(eps),
-                                 _ptr(ws), ws.numel(), _ptr(status), _stream_ptr(x.device))
-    _lib.check(rc, f"dlrb200_forward(M={M}, d={d}, r={r}, L={L})")
+                                 _ptr(ent.ws), ent.ws.numel(), _ptr(ent.status), _stream_ptr(x.device))
+        _lib.check(rc, f"dlrb200_forward(M={M}, d={d}, r={r}, L={L})")
+        _mirror_status(lib, ent, x.device)
     return y2.view(x.shape)
 
 
@@ -113,11 +154,12 @@ def forward_host(x_host: torch.Tensor, y_host: torch.Tensor, x_dev: torch.Tensor
     lib = _lib.load()
     with torch.cuda.device(Vp.device):
         need = lib.dlrb200_workspace_bytes(M, d, r, L)
-        ws, status = _workspace(Vp.device, need)
+        ent = _workspace(Vp.device, need)
         rc = lib.dlrb200_forward_host(_ptr(x_host), _ptr(y_host), _ptr(x_dev), _ptr(y_dev), _ptr(Vp), _ptr(Up),
-                                      M, d, r, L, float(eps), _ptr(ws), ws.numel(), _ptr(status),
+                                      M, d, r, L, float(eps), _ptr(ent.ws), ent.ws.numel(), _ptr(ent.status),
                                       _stream_ptr(Vp.device))
-    _lib.check(rc, "dlrb200_forward_host")
+        _lib.check(rc, "dlrb200_forward_host")
+        _mirror_status(lib, ent, Vp.device)
 
 
 def query(M: int, d: int, r: int, L: int) -> _lib.Plan:

@@ -44,8 +44,14 @@ class PackedNet:
         return ops.forward_folded(x, self.Vp, self.Up, self.eps)
 
 
-def pack_state_dict(sd: dict, device, eps: float = 1e-6) -> PackedNet:
-    """Fold one net's ``state_dict`` (keys ``Vs.i``, ``Us.i``, ``rms_w.i``, ``alphas.i``) on ``device``."""
+def pack_state_dict(sd: dict, device, eps: float = 1e-6, dtype: torch.dtype = torch.bfloat16) -> PackedNet:
+    """Fold one net's ``state_dict`` (keys ``Vs.i``, ``Us.i``, ``rms_w.i``, ``alphas.i``) on ``device``.
+
+    Every tensor, alpha included, is first rounded to ``dtype``, the dtype the serving module would hold
+    it in: the reference writes fp32 ``layerNN.pt`` files (dlr_lock/distill_logits.py:196-200) and loads
+    them into a bf16 module (``replace_layer_mlp`` casts to the layer's dtype, dlr_lock/model.py:171-172)
+    before its packer runs, so alpha reaches the fold as a bf16 value.  The result is then bit-identical to
+    ``DLRNet.folded_weights()`` of a module loaded from the same file."""
     groups = {"Vs": {}, "Us": {}, "rms_w": {}, "alphas": {}}
     for k, v in sd.items():
         m = _KEY.match(k)
@@ -54,7 +60,7 @@ def pack_state_dict(sd: dict, device, eps: float = 1e-6) -> PackedNet:
     L = len(groups["Vs"])
     if L == 0 or any(len(g) != L or sorted(g) != list(range(L)) for g in groups.values()):
         raise ValueError("not a DLR-Net state dict: need Vs.i, Us.i, rms_w.i, alphas.i for i = 0..L-1")
-    stack = lambda name: torch.stack([groups[name][i] for i in range(L)]).to(device, non_blocking=True)
+    stack = lambda name: torch.stack([groups[name][i] for i in range(L)]).to(dtype).to(device, non_blocking=True)
     Vp, Up = ops.fold_weights(stack("Vs"), stack("Us"), stack("rms_w"), stack("alphas"))
     return PackedNet(Vp, Up, eps)
 
@@ -79,7 +85,8 @@ def load_packed_weights(checkpoint_dir: str, device, n_layers: Optional[int] = N
         cached = _cache_path(checkpoint_dir, li)
         if use_cache and os.path.exists(cached) and os.path.getmtime(cached) >= os.path.getmtime(src):
             blob = torch.load(cached, map_location=device, weights_only=True)
-            nets.append(PackedNet(blob["Vp"], blob["Up"], float(blob["eps"])))
+            # the folded stacks do not depend on epsilon: the caller's value applies, not the one stored
+            nets.append(PackedNet(blob["Vp"], blob["Up"], eps))
             continue
         sd = torch.load(src, map_location="cpu", weights_only=True)
         net = pack_state_dict(sd, device, eps)

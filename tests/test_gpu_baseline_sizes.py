@@ -1,0 +1,98 @@
+"""Default routing at the benchmark configurations' own sizes, full depth, against the oracle.
+
+Each case runs the whole batch on the GPU exactly as ``bench.py`` launches it (no forced path), checks that
+``dlrb200_query`` reports the plan the test table expects, and compares rows taken from the first, a middle
+and the last row tile with both oracles computed on the CPU for those rows only:
+
+* O1 = the reference's own bf16 forward (dlr_lock/model.py:93-101 in bf16),
+* O2 = the same loop in fp32 on the same bf16 weights and input.
+
+Gates (relative L2 after the full stack; form of kernels/bench/bench_paper.py:122-133): total error <= 1e-2
+against both, and the error of the *update* y - x, which an identity kernel fails with a score of 1.0:
+<= 0.3 against O1 where the kernel carries the activation in bf16 between layers (as the reference's bf16
+forward does), <= 8e-2 against bf16-rounded O2 where it carries it in fp32.
+"""
+import pytest
+import torch
+
+from oracle import dlrnet_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_TOTAL = 1e-2
+TOL_UPDATE_BF16H = 0.3
+TOL_UPDATE_FP32H = 8e-2
+
+CFG = {  # d, r, L, seed  (the four single-net benchmark configurations)
+    "cfg1": (1024, 32, 141, 0),
+    "cfg2": (2048, 64, 142, 1),
+    "cfg3": (4096, 128, 143, 2),
+    "cfg4": (5120, 256, 149, 3),
+}
+
+STRIPED, CLUSTER, CLUSTER_SMALL, STREAMED = 1, 2, 3, 4
+
+# (configuration, rows, expected path, expected cluster size or None, expected grid or None)
+CASES = [
+    ("cfg1", 2048, CLUSTER, 2, None),
+    ("cfg2", 1, STRIPED, 1, 32),
+    ("cfg2", 4, STRIPED, 1, 32),
+    ("cfg2", 16, STRIPED, 1, 32),
+    ("cfg2", 64, None, None, None),
+    ("cfg3", 1, STRIPED, 1, 64),
+    ("cfg3", 16, STRIPED, 1, 64),
+    ("cfg3", 64, None, None, None),
+    ("cfg3", 1024, None, None, None),
+    ("cfg3", 4096, STREAMED, None, None),
+    ("cfg3", 8192, STREAMED, None, 128),
+    ("cfg4", 1, STRIPED, 1, 80),
+    ("cfg4", 64, STRIPED, 1, 80),
+    ("cfg4", 4096, STREAMED, None, None),
+]
+
+
+def _sample_rows(M: int) -> torch.Tensor:
+    """All rows of a small batch; otherwise 96 rows from each of the first, a middle and the last row tile
+    (tile boundaries included)."""
+    if M <= 288:
+        return torch.arange(M)
+    mid = (M // 2 // 128) * 128
+    return torch.cat([torch.arange(0, 96), torch.arange(mid + 16, mid + 112), torch.arange(M - 96, M)])
+
+
+@pytest.mark.parametrize("cfg,M,path,cluster,grid", CASES, ids=[f"{c[0]}-M{c[1]}" for c in CASES])
+def test_default_routing_at_benchmark_sizes(cfg, M, path, cluster, grid):
+    import dlr_lock_b200 as D
+    D.ops._lib.load()
+    d, r, L, seed = CFG[cfg]
+    dev = torch.device("cuda:0")
+    p, x = O.seeded_case(d, r, L, M, seed, alpha=0.01)
+    plan = D.ops.query(M, d, r, L)
+    if path is not None:
+        assert plan.path == path, (plan.path, plan.cluster, plan.grid)
+    if cluster is not None:
+        assert plan.cluster == cluster
+    if grid is not None:
+        assert plan.grid == grid
+    Vp, Up = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    xd = x.to(dev)
+    y = D.ops.forward_folded(xd, Vp, Up, p.eps)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert torch.equal(xd.cpu(), x)                     # the input is not modified
+    rows = _sample_rows(M)
+    ys, xs = y[rows.to(dev)].cpu(), x[rows]
+    o1 = O.forward_eager(xs, p)
+    o2 = O.forward_fp32(xs, p)
+    e1, e2 = O.rel_l2(ys, o1), O.rel_l2(ys, o2)
+    assert e1 <= TOL_TOTAL and e2 <= TOL_TOTAL, (e1, e2)
+    if plan.path in (CLUSTER, STREAMED):
+        eu = O.rel_l2_update(ys, o1, xs)
+        assert eu <= TOL_UPDATE_BF16H, eu
+    else:
+        eu = O.rel_l2_update_q(ys, o2, xs)
+        assert eu <= TOL_UPDATE_FP32H, eu
+    # the rest of the batch went through the same stack: it moved, and by about as much as the sampled rows
+    moved_all = O.rel_l2(y.cpu(), x)
+    moved_rows = O.rel_l2(ys, xs)
+    assert 0.5 * moved_rows <= moved_all <= 2.0 * moved_rows, (moved_all, moved_rows)

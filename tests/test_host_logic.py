@@ -121,3 +121,49 @@ def test_surgery_and_checkpoint_round_trip(tmp_path):
     assert torch.allclose(logits, again, atol=1e-6)
     assert D.set_checkpointing(fresh, False) == 2
     assert D.accelerate_locked_model(fresh) == 2
+
+
+def test_fast_path_is_refused_whenever_a_gradient_could_be_asked_for():
+    # eval mode + grad enabled + trainable parameters: the library's output would be detached from the
+    # parameters, so the module must take the torch loop (dlr_lock/model.py:88-101 always builds the graph)
+    net = D.DLRNet(64, 8, 3, alpha_init=0.1).to(torch.bfloat16).eval()
+    x = torch.randn(2, 64, dtype=torch.bfloat16)
+
+    class X:      # what _fast_ok looks at, standing in for a CUDA bf16 input on a machine without a GPU
+        is_cuda, dtype, requires_grad = True, torch.bfloat16, False
+    with torch.enable_grad():
+        assert net._fast_ok(X) is False                    # parameters require grad, eval mode
+        net.Vs[0].requires_grad_(False)
+        assert net._fast_ok(X) is False                    # first V frozen, the others still train
+        for p in net.parameters():
+            p.requires_grad_(False)
+        assert net._fast_ok(X) is True
+        X.requires_grad = True
+        assert net._fast_ok(X) is False
+    with torch.no_grad():
+        for p in net.parameters():
+            p.requires_grad_(True)
+        X.requires_grad = False
+        assert net._fast_ok(X) is True                     # inference: nothing can ask for a gradient
+    # and the torch loop it falls back to does carry gradients to a middle layer's parameters
+    net.train()
+    net(x).float().sum().backward()
+    assert net.Us[1].grad is not None
+
+
+def test_folded_cache_key_sees_an_edit_of_any_layer():
+    net = D.DLRNet(64, 8, 5, alpha_init=0.1)
+    k0 = net._cache_key()
+    with torch.no_grad():
+        net.rms_w[2].mul_(1.5)                             # in-place edit of a middle layer
+    k1 = net._cache_key()
+    assert k1 != k0
+    with torch.no_grad():
+        net.alphas[3].fill_(0.3)
+    assert net._cache_key() != k1
+    k2 = net._cache_key()
+    net.Vs[1].data.copy_(torch.zeros_like(net.Vs[1]))      # bypasses the version counter: documented, needs invalidate()
+    assert net._cache_key() == k2
+    net._folded = ("sentinel",)
+    net.invalidate()
+    assert net._folded is None

@@ -12,7 +12,7 @@ from oracle import build_oracle
 from conftest import GOLDEN, load_golden
 
 SMALL = ["toy_d64_r8", "toy_d256_r32", "toy_d256_r32_stress", "toy_d512_r64_stress"]
-FULL = ["cfg1_d1024_r32", "cfg1_d1024_r32_stress", "cfg2_d2048_r64", "cfg3_d4096_r128"]
+FULL = ["cfg1_d1024_r32", "cfg1_d1024_r32_stress", "cfg2_d2048_r64", "cfg3_d4096_r128", "cfg4_d5120_r256"]
 
 
 def _case(name):

@@ -37,10 +37,18 @@ def test_static_entry_point_matches_regular_one_twice(d, r, L, M, monkeypatch):
     for call, xd in enumerate(xs):                      # two calls in a row share the built-in scratch
         want = D.ops.forward_folded(xd, Vp, Up, p.eps)
         got = torch.empty_like(xd)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(dev)       # the driver's count: sees any cudaMalloc, torch's or not
+        torch_before = torch.cuda.memory_allocated(dev)
         rc = lib.dlrb200_forward_static(_vp(xd), _vp(got), _vp(Vp), _vp(Up), M, d, r, L, ctypes.c_float(p.eps),
                                         _vp(status), stream)
         assert rc == 0, lib.dlrb200_strerror(rc)
         torch.cuda.synchronize()
+        if call > 0:
+            # the property in the entry point's name: no device memory was taken, by any allocator (the very
+            # first call on a device may still load the kernel's module, which the driver accounts as memory)
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
+        assert torch.cuda.memory_allocated(dev) == torch_before
         assert int(status.item()) == 0
         assert O.rel_l2(got.cpu(), want.cpu()) <= TOL, f"call {call}"
         assert O.rel_l2(got.cpu(), O.forward_fp32(x[call * M:(call + 1) * M], p)) <= 5e-3
