@@ -8,6 +8,7 @@
 #include "decode.h"
 #include "decode_cluster.h"
 #include "stream.h"
+#include "stream_pair.h"
 
 namespace {
 
@@ -246,9 +247,21 @@ bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
     return streamed;
 }
 
+// The streamed kernel on CTA pairs: same data flow as the streamed kernel, half the weight bytes through each
+// SM's shared memory.
+bool use_pair_path(int M, int d, int r, int L, const DevInfo& di) {
+    const int forced = env_int("DLRB200_FORCE_PATH", 0);
+    if (M <= 64 || !dlr::stream_pair_supported(d, r)) return false;
+    if (forced == DLRB200_PATH_STREAMED_PAIRS) return true;
+    (void)L; (void)di;
+    return false;
+}
+
 bool use_cluster_path(int M, int d, int r, int L) {
     const int forced = env_int("DLRB200_FORCE_PATH", 0);
-    if (forced == DLRB200_PATH_STRIPED || forced == DLRB200_PATH_STREAMED || forced == DLRB200_PATH_CLUSTER_SMALL) return false;
+    if (forced == DLRB200_PATH_STRIPED || forced == DLRB200_PATH_STREAMED || forced == DLRB200_PATH_CLUSTER_SMALL ||
+        forced == DLRB200_PATH_STREAMED_PAIRS)
+        return false;
     if (!dlr::cluster_supported(d, r, L)) return false;
     if (forced == DLRB200_PATH_CLUSTER) return true;
     // One 128-row tile on one cluster costs the same for any M <= 128 (1.16 ms at d = 4096, r = 128, L = 143),
@@ -342,6 +355,7 @@ int dlrb200_query(int M, int d, int r, int L, dlrb200_plan* plan) {
     if (rc != DLRB200_OK) return rc;
     std::memset(plan, 0, sizeof(*plan));
     plan->workspace_bytes = dlrb200_workspace_bytes(M, d, r, L);
+    if (use_pair_path(M, d, r, L, di)) return dlr::stream_pair_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
     if (use_stream_path(M, d, r, L, di)) return dlr::stream_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
     if (use_cluster_path(M, d, r, L)) return dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
     if (use_cluster_small(M, d, r)) return dlr::decode_cluster_plan(M, d, r, L, di.smem_optin, plan);
@@ -371,6 +385,17 @@ int dlrb200_forward(const void* x, void* y, const void* Vp, const void* Up, int 
     if (rc != DLRB200_OK) return rc;
     if (di.cc_major != 10) return DLRB200_ERR_CUDA;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (use_pair_path(M, d, r, L, di) && dlr::stream_aligned(x, y)) {
+        EncodeTiledFn enc = encode_fn();
+        if (!enc) return DLRB200_ERR_CUDA;
+        rc = dlr::stream_pair_forward(reinterpret_cast<void*>(enc), x, y, Vp, Up, M, d, r, L, eps, status_dev, st, di.num_sms,
+                                      di.smem_optin, spin_limit(),
+                                      env_int("DLRB200_PROFILE", 0) ? reinterpret_cast<unsigned long long*>(
+                                                                          static_cast<uint8_t*>(workspace) + 256)
+                                                                    : nullptr);
+        if (rc == DLRB200_ERR_CUDA) g_last_cuda_error = int(cudaGetLastError());
+        return rc;
+    }
     if (use_stream_path(M, d, r, L, di) && dlr::stream_aligned(x, y)) {
         EncodeTiledFn enc = encode_fn();
         if (!enc) return DLRB200_ERR_CUDA;

@@ -65,6 +65,13 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster) {
                  : "memory");
 }
 
+// Arrive on a barrier of another CTA without the cluster-scope release: for signals whose payload is not
+// ordinary memory (tensor memory already made consistent with tcgen05.wait and tcgen05.fence, or registers
+// already consumed).  The cluster-scope release above costs the issuing thread about a thousand cycles.
+__device__ __forceinline__ void mbar_arrive_remote_light(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -402,6 +409,13 @@ __device__ __forceinline__ void st_async_v4(uint32_t dst_cluster, uint32_t a, ui
                  : "memory");
 }
 
+// The same for one 32-bit word.
+__device__ __forceinline__ void st_async_b32(uint32_t dst_cluster, uint32_t a, uint32_t bar_cluster) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(dst_cluster), "r"(a),
+                 "r"(bar_cluster)
+                 : "memory");
+}
+
 // Bounded waits on mbarriers that also give up when another thread of the CTA has
 // raised the abort flag (a word in shared memory).
 struct Waiter {
@@ -444,5 +458,77 @@ __device__ __forceinline__ void bulk_wait_group() {
 }
 // Order generic-proxy accesses (any state space) against later async-proxy ones.
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
+// tcgen05 with cta_group::2: the two CTAs of a pair (cluster ranks 2k and 2k+1)
+// drive one tensor-core instruction of M = 256 rows.  Each CTA keeps its own 128
+// rows of the A operand and of the accumulator in its own tensor memory (same
+// addresses in both) and supplies half of the B operand's N rows from its own
+// shared memory (same offsets in both).  One thread of the even-ranked CTA (the
+// leader) issues; completion is signalled to barriers at the same offset in
+// either or both CTAs.  A kernel uses one cta_group for all its tcgen05
+// instructions.
+// ---------------------------------------------------------------------------
+// One warp of EACH CTA of the pair executes alloc / relinquish / dealloc.
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+
+// D[tmem, both CTAs] (+)= A[tmem, both CTAs] * B[smem halves of both CTAs]; M = 256.
+__device__ __forceinline__ void umma_ts2(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Completion of all tcgen05 work issued so far by this thread arrives on the barrier
+// at this shared-memory offset in every CTA of `cta_mask` (bit = rank in the cluster).
+__device__ __forceinline__ void umma_commit2_mask(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(cta_mask)
+                 : "memory");
+}
+// ... on this CTA's barrier only.
+__device__ __forceinline__ void umma_commit2(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+// Tiled 2-D load into THIS CTA's shared memory whose bytes are counted on a barrier
+// that may live in the other CTA of the pair (`bar_cluster`: a shared::cluster address
+// from mapa()).  One destination, no multicast: each CTA fetches its own half.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster)
+        : "memory");
+}
+
+// Non-blocking test of an mbarrier phase (try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 
 }  // namespace dlr
