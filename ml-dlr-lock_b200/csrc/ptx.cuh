@@ -428,6 +428,17 @@ struct Waiter {
         }
         return false;
     }
+    // Whole warp, every lane with a barrier and parity of its own (lanes may name the same one): one poll
+    // covers several barriers at the latency of one.  Returns true once every lane's phase is complete.
+    __device__ __forceinline__ bool warp(uint32_t bar, uint32_t parity) const {
+        bool done = false;
+        for (uint32_t i = 0; i < limit; ++i) {
+            if (!done) done = mbar_try_wait(bar, parity);
+            if (__all_sync(0xffffffffu, done)) return true;
+            if ((i & 63u) == 63u && *abort_flag) return false;
+        }
+        return false;
+    }
     __device__ __forceinline__ bool cluster(uint32_t bar, uint32_t parity) const {
         for (uint32_t i = 0; i < limit; ++i) {
             if (mbar_try_wait_cluster(bar, parity)) return true;

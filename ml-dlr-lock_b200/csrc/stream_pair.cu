@@ -58,10 +58,14 @@ constexpr int kNLP = 2;                  // slots the old values of a chunk are 
 constexpr int kNSP = 2;                  // slots the new values are written to and stored from
 constexpr int kHBytesP = 2 * 16384;      // one chunk: two tiles of 128 rows x 64 columns (128-byte swizzle)
 
-// Tensor-memory columns (per CTA): z [0, R) | s [128, 128 + R/2) | A [192, 256) | dh0 [256, 384) | dh1 [384, 512).
+// Tensor-memory columns (per CTA): z [0, R) | s [128, 128 + R/2) | buffer 0 [256, 384) | buffer 1 [384, 512).
+// A buffer first holds dh of a chunk (fp32, 128 columns); the epilogue thread that has read its 32 columns of
+// dh writes its 32 updated values back as bf16 over the first 16 of them, and the V contraction reads the
+// chunk from there (K step k: columns 32 (k / 2) + 8 (k % 2)).  The chunk therefore needs no buffer of its
+// own, two chunks are in flight, and the epilogue never waits for the V contraction of the chunk before.
 template <int R>
 struct PCfg {
-    static constexpr uint32_t Z_COL = 0, S_COL = 128, A_COL = 192, BUF_COL = 256;
+    static constexpr uint32_t Z_COL = 0, S_COL = 128, BUF_COL = 256;
     // this CTA's half of a chunk's U' rows: 64 rows x R K-columns, in tiles of 64 K-columns
     static constexpr int UT = R / 64;
     static constexpr int U_TILE_BYTES = 64 * 128;
@@ -89,9 +93,8 @@ struct PBars {
     uint64_t s_written[kNSP];    // the 16 epilogue warps have written the new chunk
     uint64_t s_empty[kNSP];      // the store warp's bulk copy has read it
     uint64_t dh_full[2];         // commit, both CTAs: dh of the chunk is in the buffer
-    uint64_t dh_empty[2];        // leader: the 32 epilogue warps of the pair have read dh
-    uint64_t a_ready;            // leader: the 32 epilogue warps have put the updated chunk (bf16) into tensor memory
-    uint64_t a_empty;            // commit, both CTAs: the chunk has been read
+    uint64_t a_ready[2];         // leader: the 32 epilogue warps have put the updated chunk (bf16) into the buffer
+    uint64_t a_free[2];          // commit, both CTAs: the V contraction has read the chunk, the buffer is free
     uint64_t z_full;             // commit, both CTAs
     uint64_t s_ready;            // leader: 32 epilogue warps
     uint64_t xchg_bar;           // two pairs: the other pair's message has arrived (bytes)
@@ -112,11 +115,19 @@ struct PParams {
     float eps, inv_d;
     int* status;
     unsigned int spin_limit;
-    unsigned long long* prof; // optional cycle counters (debug), or null
+    unsigned long long* prof; // time stamps (profiling instantiation), or null
+    int trace_layer;
+    int exp;                  // profiling instantiation only: bits that leave out one piece of work each (timing experiments)
 };
 
-// cycle counters exist only in the profiling instantiation: they cost two dozen registers
-#define DLP_CLK() (PROF ? clock64() : 0ll)
+// Time stamps of one layer of the first pair of the grid, written only by the profiling instantiation:
+// prof[(CTA * 8 + role) * 256 + chunk * 8 + event] = clock64().  Roles: 0-2 producer (activations, U', V'),
+// 3 U-MMA, 4 V-MMA, 5 store, 6 and 7 the first and the last epilogue warp.
+#define DLP_T(role, layer, chunk, event)                                                                   \
+    do {                                                                                                   \
+        if (PROF && blockIdx.x < 2 && (layer) == p.trace_layer && (chunk) < 32)                            \
+            p.prof[((blockIdx.x * 8 + (role)) * 32 + (chunk)) * 8 + (event)] = (unsigned long long)clock64(); \
+    } while (0)
 
 template <int R, bool PROF>
 __global__ void __launch_bounds__(kThreadsP, 1)
@@ -124,7 +135,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmU, PParams p) {
     using C = PCfg<R>;
     constexpr uint32_t NU = C::NU, NV = C::NV;
-    constexpr uint32_t kZCol = C::Z_COL, kSCol = C::S_COL, kACol = C::A_COL, kBufCol = C::BUF_COL;
+    constexpr uint32_t kZCol = C::Z_COL, kSCol = C::S_COL, kBufCol = C::BUF_COL;
     // the swizzled tiles need a 1024-byte aligned base: asked for here, checked below
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* lbuf = smem;
@@ -167,10 +178,9 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars->dh_full[b]), 1);
-            mbar_init(smem_u32(&bars->dh_empty[b]), 2 * kEpiWarpsP);
+            mbar_init(smem_u32(&bars->a_ready[b]), 2 * kEpiWarpsP);
+            mbar_init(smem_u32(&bars->a_free[b]), 1);
         }
-        mbar_init(smem_u32(&bars->a_ready), 2 * kEpiWarpsP);
-        mbar_init(smem_u32(&bars->a_empty), 1);
         mbar_init(smem_u32(&bars->z_full), 1);
         mbar_init(smem_u32(&bars->s_ready), 2 * kEpiWarpsP);
         mbar_init(smem_u32(&bars->xchg_bar), 1);
@@ -236,6 +246,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     const uint32_t dst = lbuf_s + hp.st * kHBytesP;
                     const CUtensorMap* src = hq >= 1 ? &tmY : &tmX;
                     const int m0 = (cl + ht * ncl) * 2 * kRowsP + hf * kRowsP;
+                    DLP_T(0, hq, hc, 0);
                     mbar_arrive_expect_tx(bar, kHBytesP);
                     tma_load_2d(dst, src, col0 + hc * kCWP, m0, bar);
                     tma_load_2d(dst + 16384, src, col0 + hc * kCWP + 64, m0, bar);
@@ -247,6 +258,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                 }
                 if (nu < total_w && mbar_test(smem_u32(&bars->u_empty[up.st]), up.ph ^ 1u)) {
                     const uint32_t dst = ubuf_s + up.st * C::U_BYTES;
+                    DLP_T(1, uq, uc, 0);
                     if (hf == 0) mbar_arrive_expect_tx(smem_u32(&bars->u_full[up.st]), 2 * C::U_BYTES);
 #pragma unroll
                     for (int t = 0; t < C::UT; ++t)
@@ -260,6 +272,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                 }
                 if (nv < total_w && mbar_test(smem_u32(&bars->v_empty[vp.st]), vp.ph ^ 1u)) {
                     const uint32_t dst = vbuf_s + vp.st * C::V_BYTES;
+                    DLP_T(2, vq - 1, vc, 0);
                     if (hf == 0) mbar_arrive_expect_tx(smem_u32(&bars->v_full[vp.st]), 2 * C::V_BYTES);
 #pragma unroll
                     for (int t = 0; t < 2; ++t)
@@ -299,24 +312,24 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             RingPos up;
             uint32_t n = 0;
             uint32_t c_s = 0;
-            long long mw[3] = {0, 0, 0};
             for (int t = 0; t < my_tiles && !err; ++t) {
+                n += uint32_t(nch);          // the pass over x goes through the buffers too (chunk n: buffer n & 1)
                 for (int q = 0; q < p.L && !err; ++q) {
                     err_layer = q;
-                    long long t0 = DLP_CLK();
+                    DLP_T(3, q, 0, 7);
                     if (!w.cluster(smem_u32(&bars->s_ready), c_s & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    DLP_T(3, q, 0, 0);
                     ++c_s;
                     tc_fence_after();
-                    mw[0] += DLP_CLK() - t0;
                     for (int c = 0; c < nch; ++c, ++n) {
                         const uint32_t b = n & 1u;
-                        t0 = DLP_CLK();
-                        if (!w.cluster(smem_u32(&bars->dh_empty[b]), ((n >> 1) & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        mw[2] += DLP_CLK() - t0;
-                        const uint32_t acc = tmem_base + kBufCol + b * 128u;
-                        t0 = DLP_CLK();
+                        // the weights land early: wait for them first, off the critical path
                         if (!w.cluster(smem_u32(&bars->u_full[up.st]), up.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
-                        mw[1] += DLP_CLK() - t0;
+                        DLP_T(3, q, c, 1);
+                        const uint32_t acc = tmem_base + kBufCol + b * 128u;
+                        // the buffer is free once the V contraction of the chunk two before has read it
+                        if (!w.cta(smem_u32(&bars->a_free[b]), ((n >> 1) & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        DLP_T(3, q, c, 2);
                         tc_fence_after();
                         const uint32_t ub = ubuf_s + up.st * C::U_BYTES;
 #pragma unroll
@@ -327,12 +340,12 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                         umma_commit2_mask(smem_u32(&bars->u_empty[up.st]), pair_mask);
                         up.step(NU);
                         umma_commit2_mask(smem_u32(&bars->dh_full[b]), pair_mask);
+                        DLP_T(3, q, c, 3);
                     }
                 }
             }
             umma_commit2(smem_u32(&bars->drain[0]));
             mbar_wait(smem_u32(&bars->drain[0]), 0, kDrainPolls);
-            if (PROF) for (int k = 0; k < 3; ++k) p.prof[blockIdx.x * 32 + 4 + k] = (unsigned long long)mw[k];
         }
     } else if (warp == 2) {
         // =============================== V-MMA warp (leader) =======================
@@ -341,33 +354,32 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             constexpr uint32_t idesc_v = umma_idesc_bf16(256, R);
             RingPos vp;
             uint32_t n = 0;
-            long long mw[2] = {0, 0};
             for (int t = 0; t < my_tiles && !err; ++t) {
                 for (int q = -1; q < p.L && !err; ++q) {
                     err_layer = q;
                     const bool feeds = q + 1 < p.L;
                     for (int c = 0; c < nch; ++c, ++n) {
-                        long long t0 = DLP_CLK();
-                        if (!w.cluster(smem_u32(&bars->a_ready), n & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        mw[0] += DLP_CLK() - t0;
+                        const uint32_t b = n & 1u;
+                        // the weights land early: wait for them first, off the critical path
+                        if (feeds && !w.cluster(smem_u32(&bars->v_full[vp.st]), vp.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
+                        DLP_T(4, q, c, 1);
+                        if (!w.cluster(smem_u32(&bars->a_ready[b]), (n >> 1) & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        DLP_T(4, q, c, 2);
                         tc_fence_after();
                         if (feeds) {
-                            const uint32_t a0 = tmem_base + kACol;
-                            t0 = DLP_CLK();
-                            if (!w.cluster(smem_u32(&bars->v_full[vp.st]), vp.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
-                            mw[1] += DLP_CLK() - t0;
-                            tc_fence_after();
+                            const uint32_t a0 = tmem_base + kBufCol + b * 128u;
                             const uint32_t vb = vbuf_s + vp.st * C::V_BYTES;
 #pragma unroll
                             for (int k = 0; k < kCWP / 16; ++k) {
                                 const uint64_t bdesc = umma_desc(vb + uint32_t(k / 4) * C::V_TILE_BYTES, 2u, 1024u) + uint64_t(2 * (k % 4));
-                                umma_ts2(tmem_base + kZCol, a0 + uint32_t(8 * k), bdesc, idesc_v, (c | k) ? 1u : 0u);
+                                umma_ts2(tmem_base + kZCol, a0 + uint32_t(32 * (k / 2) + 8 * (k % 2)), bdesc, idesc_v, (c | k) ? 1u : 0u);
                             }
                             umma_commit2_mask(smem_u32(&bars->v_empty[vp.st]), pair_mask);
                             vp.step(NV);
                         }
                         // the chunk has been read (last layer: nothing reads it, the commit arrives at once)
-                        umma_commit2_mask(smem_u32(&bars->a_empty), pair_mask);
+                        umma_commit2_mask(smem_u32(&bars->a_free[b]), pair_mask);
+                        DLP_T(4, q, c, 3);
                     }
                     if (err) break;
                     if (feeds) umma_commit2_mask(smem_u32(&bars->z_full), pair_mask);
@@ -375,7 +387,6 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             }
             umma_commit2(smem_u32(&bars->drain[1]));
             mbar_wait(smem_u32(&bars->drain[1]), 0, kDrainPolls);
-            if (PROF) for (int k = 0; k < 2; ++k) p.prof[blockIdx.x * 32 + 8 + k] = (unsigned long long)mw[k];
         }
     } else if (warp == 3) {
         // =============================== store warp ================================
@@ -395,13 +406,15 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     err_layer = q;
                     for (int c = 0; c < nch; ++c, ++n) {
                         if (!w.cta(smem_u32(&bars->s_written[sp.st]), sp.ph)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        if (m0 < p.M) {              // a CTA whose rows lie wholly past the batch stores nothing
+                        DLP_T(5, q, c, 0);
+                        if (m0 < p.M && !(PROF && (p.exp & 8))) {   // a CTA whose rows lie wholly past the batch stores nothing
                             const uint32_t src = sbuf_s + sp.st * kHBytesP;
                             tma_store_2d(&tmY, col0 + c * kCWP, m0, src);
                             tma_store_2d(&tmY, col0 + c * kCWP + 64, m0, src + 16384);
                         }
                         bulk_commit_group();
                         bulk_wait_group_read<0>();
+                        DLP_T(5, q, c, 1);
                         mbar_arrive(smem_u32(&bars->s_empty[sp.st]));
                         sp.step(kNSP);
                         bulk_wait_group<2>();            // every group but the last two is complete
@@ -423,12 +436,10 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
         const int et = int(threadIdx.x) - 128;            // = cq * 128 + er
         const uint32_t tl = tmem_base + (uint32_t(32 * q4) << 16);
         uint32_t n = 0;                      // chunks seen (all passes): phase of the A operand's barriers
-        uint32_t nu = 0;                     // chunks of update passes: accumulator nu & 1
+        uint32_t du0 = 0, du1 = 0;           // times each buffer has received a dh: phase of its dh_full barrier
         uint32_t c_z = 0;
-        long long ew[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
         // barriers of the leader that this warp signals: its own if this CTA leads, else through the cluster window
-        const uint32_t l_dh_empty = hf ? mapa(smem_u32(&bars->dh_empty[0]), lead) : smem_u32(&bars->dh_empty[0]);
-        const uint32_t l_a_ready = hf ? mapa(smem_u32(&bars->a_ready), lead) : smem_u32(&bars->a_ready);
+        const uint32_t l_a_ready = hf ? mapa(smem_u32(&bars->a_ready[0]), lead) : smem_u32(&bars->a_ready[0]);
         const uint32_t l_s_ready = hf ? mapa(smem_u32(&bars->s_ready), lead) : smem_u32(&bars->s_ready);
         auto arrive_lead = [&](uint32_t bar) {
             if (hf) mbar_arrive_remote_light(bar);
@@ -441,6 +452,8 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
         const uint32_t p_xack = pp > 1 ? mapa(smem_u32(&bars->xack_bar), partner) : 0u;
 
         RingPos lp, sp;
+        const int trole = (warp == 4 && lane == 0) ? 6 : ((warp == 19 && lane == 0) ? 7 : -1);
+#define DLP_TE(layer, chunk, event) do { if (PROF && trole >= 0) DLP_T(trole, layer, chunk, event); } while (0)
         const uint32_t x7 = uint32_t(er & 7);
         // this thread's 64 bytes of its row inside a staging slot: tile cq / 2, 16-byte pieces 4 (cq % 2) .. + 3
         const uint32_t row_off = uint32_t((cq >> 1) * 16384 + er * 128);
@@ -450,17 +463,33 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             for (int q = -1; q < p.L && !err; ++q) {
                 err_layer = q;
                 for (int c = 0; c < nch; ++c, ++n) {
-                    const uint32_t b = nu & 1u;
-                    const uint32_t buf = tl + kBufCol + b * 128u + uint32_t(32 * cq);
+                    const uint32_t b = n & 1u;
+                    const uint32_t buf = tl + kBufCol + b * 128u + uint32_t(32 * cq);   // this thread's 32 columns of the buffer
                     // ---- old values of the chunk: this thread's 64 bytes of its row, from the staging slot
-                    long long t0 = DLP_CLK();
-                    if (!w.cta(smem_u32(&bars->l_full[lp.st]), lp.ph)) { err = DLRB200_ERR_TIMEOUT_COPY; break; }
-                    ew[4] += DLP_CLK() - t0;
+                    DLP_TE(q, c, 0);
+                    // ---- everything this chunk needs, in one poll: lane 1 watches the buffer (dh has arrived; in
+                    // the pass over x: the V contraction of the chunk two before has read it, which dh_full implies
+                    // later), lane 2 the store slot, the other lanes the old values of the chunk
+                    {
+                        uint32_t wbar = smem_u32(&bars->l_full[lp.st]), wpar = lp.ph;
+                        if (lane == 1) {
+                            wbar = q >= 0 ? smem_u32(&bars->dh_full[b]) : smem_u32(&bars->a_free[b]);
+                            wpar = q >= 0 ? ((b ? du1 : du0) & 1u) : (((n >> 1) & 1u) ^ 1u);
+                        } else if (lane == 2 && q >= 0) {
+                            wbar = smem_u32(&bars->s_empty[sp.st]);
+                            wpar = sp.ph ^ 1u;
+                        }
+                        if (!w.warp(wbar, wpar)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    }
+                    tc_fence_after();
+                    DLP_TE(q, c, 1);
                     uint32_t cur[16];
                     {
                         const uint8_t* rowp = lbuf + lp.st * kHBytesP + row_off;
+                        if (PROF && (p.exp & 1)) rowp = lbuf + lane * 16;     // experiment: no bank-spread reads
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
+                            if (PROF && (p.exp & 2)) { cur[4 * j] = cur[4 * j + 1] = cur[4 * j + 2] = cur[4 * j + 3] = 0x3f803f80u; continue; }
                             const uint4 hv = *reinterpret_cast<const uint4*>(rowp + (((piece0 + uint32_t(j)) ^ x7) << 4));
                             cur[4 * j] = hv.x; cur[4 * j + 1] = hv.y; cur[4 * j + 2] = hv.z; cur[4 * j + 3] = hv.w;
                         }
@@ -469,21 +498,16 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->l_free[lp.st]));
                     lp.step(kNLP);
-                    t0 = DLP_CLK();
                     if (q >= 0) {
-                        if (!w.cluster(smem_u32(&bars->dh_full[b]), (nu >> 1) & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        ++nu;
-                        ew[1] += DLP_CLK() - t0;
-                        tc_fence_after();
+                        if (b) ++du1; else ++du0;
+                        DLP_TE(q, c, 2);
                         uint32_t dv[32];
                         tmem_ld32(buf, dv);
                         tmem_wait_ld();
-                        // dh is in registers: the U-MMA warp may overwrite the accumulator
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) arrive_lead(l_dh_empty + 8u * b);
+                        DLP_TE(q, c, 3);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
+                            if (PROF && (p.exp & 16)) { cur[j] ^= dv[2 * j] & dv[2 * j + 1]; continue; }
                             const uint32_t hw = cur[j];
                             const float f0 = bf16lo_to_f(hw) + __uint_as_float(dv[2 * j]);
                             const float f1 = bf16hi_to_f(hw) + __uint_as_float(dv[2 * j + 1]);
@@ -491,7 +515,6 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                             ssq1 = fmaf(f1, f1, ssq1);
                             cur[j] = pack_bf16x2(f0, f1);
                         }
-                        ew[0] += DLP_CLK() - t0;
                     } else {
                         // pass over x: the chunk goes to the tensor core as it is
 #pragma unroll
@@ -501,45 +524,39 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                             ssq1 = fmaf(f1, f1, ssq1);
                         }
                     }
-                    // ---- the chunk (bf16) becomes the A operand of the next layer's contraction: first, because the
-                    // tensor core waits for it
-                    const long long t2 = DLP_CLK();
-                    if (!w.cluster(smem_u32(&bars->a_empty), (n & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                    ew[5] += DLP_CLK() - t2;
-                    tc_fence_after();
-                    tmem_st16(tl + kACol + 16u * uint32_t(cq), cur);
+                    // ---- the chunk (bf16) becomes the A operand of the next layer's contraction, over this thread's own
+                    // columns of dh: first, because the tensor core waits for it
+                    DLP_TE(q, c, 4);
+                    tmem_st16(buf, cur);
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) arrive_lead(l_a_ready);
-                    ew[6] += DLP_CLK() - t2;
+                    if (lane == 0) arrive_lead(l_a_ready + 8u * b);
+                    DLP_TE(q, c, 6);
                     // ---- new values into a store slot: the store warp copies the slot out
-                    const long long t3 = DLP_CLK();
                     if (q >= 0) {
-                        if (!w.cta(smem_u32(&bars->s_empty[sp.st]), sp.ph ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                         uint8_t* rowp = sbuf + sp.st * kHBytesP + row_off;
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            *reinterpret_cast<uint4*>(rowp + (((piece0 + uint32_t(j)) ^ x7) << 4)) =
+                            if (!(PROF && (p.exp & 4))) *reinterpret_cast<uint4*>(rowp + (((piece0 + uint32_t(j)) ^ x7) << 4)) =
                                 make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
                         fence_async_smem();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&bars->s_written[sp.st]));
                         sp.step(kNSP);
                     }
-                    ew[7] += DLP_CLK() - t3;
+                    DLP_TE(q, c, 7);
                 }
                 if (err) break;
                 if (q + 1 < p.L) {
                     // ---- z(q+1) is complete after the last chunk's V contraction: s = silu(z * rstd) -> tensor memory
-                    const long long t0 = DLP_CLK();
                     constexpr int NZ = C::NZ;            // columns of z per thread: 32 (rank 128) or 16 (rank 64)
                     float ssq = ssq0 + ssq1;
                     ssq0 = ssq1 = 0.f;
+                    DLP_TE(q, 24, 0);
                     if (!w.cluster(smem_u32(&bars->z_full), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    DLP_TE(q, 24, 1);
                     tc_fence_after();
-                    const long long tb1 = DLP_CLK();
-                    ew[8] += tb1 - t0;
                     uint32_t zv[NZ];
                     if constexpr (NZ == 32) tmem_ld32(tl + kZCol + uint32_t(cq * NZ), zv);
                     else tmem_ld16(tl + kZCol + uint32_t(cq * NZ), zv);
@@ -564,10 +581,9 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                             zv[8 * k + 6] = o3 << 16; zv[8 * k + 7] = o3 & 0xffff0000u;
                         }
                         st_async_b32(p_recv_q + uint32_t(et * 4), __float_as_uint(ssq), p_xchg);
-                        const long long tb2 = DLP_CLK();
-                        ew[9] += tb2 - tb1;
+                        DLP_TE(q, 24, 2);
                         if (!w.cluster(smem_u32(&bars->xchg_bar), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        ew[10] += DLP_CLK() - tb2;
+                        DLP_TE(q, 24, 3);
                         ssq += recv_q[et];
 #pragma unroll
                         for (int k = 0; k < C::NZW; ++k) {
@@ -579,21 +595,19 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                             f[6] += bf16lo_to_f(v.w); f[7] += bf16hi_to_f(v.w);
                         }
                     }
-                    const long long tb3 = DLP_CLK();
                     ssqx[cq * kRowsP + er] = ssq;              // index et: the word this thread's received partial came in
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->ssq_bar));
                     if (!w.cta(smem_u32(&bars->ssq_bar), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                    ew[11] += DLP_CLK() - tb3;
                     // the four quarters in a fixed order: every thread of a row gets the same total
                     const float tot = (ssqx[er] + ssqx[kRowsP + er]) + (ssqx[2 * kRowsP + er] + ssqx[3 * kRowsP + er]);
                     const float rstd = rsqrtf(tot * p.inv_d + p.eps);
+                    DLP_TE(q, 24, 4);
                     if (pp > 1) {
                         // the message and the words shared with it have been read: the sender may overwrite them
                         __syncwarp();
                         if (lane == 0) mbar_arrive_remote_light(p_xack);
                     }
-                    ew[2] += DLP_CLK() - t0;
                     uint32_t sv[NZ / 2];
 #pragma unroll
                     for (int j = 0; j < NZ / 2; ++j)
@@ -605,12 +619,10 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) arrive_lead(l_s_ready);
-                    ew[3] += DLP_CLK() - t0;
+                    DLP_TE(q, 24, 5);
                 }
             }
         }
-        if (PROF && threadIdx.x == 128)
-            for (int k = 0; k < 12; ++k) p.prof[blockIdx.x * 32 + 12 + k] = (unsigned long long)ew[k];
     }
 
     // ---- leave: report, let every role arrive, free tensor memory
@@ -708,6 +720,9 @@ int launch_pair(void* enc, const void* x, void* y, const void* Vp, const void* U
     p.status = status_dev;
     p.spin_limit = spin_limit;
     p.prof = prof;
+    p.trace_layer = L / 2;
+    p.exp = 0;
+    if (const char* e = getenv("DLRB200_EXP")) p.exp = atoi(e);
     const cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, tmX, tmY, tmV, tmU, p);
     return ce == cudaSuccess ? DLRB200_OK : DLRB200_ERR_CUDA;
 }
