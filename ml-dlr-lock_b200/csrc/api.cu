@@ -190,25 +190,29 @@ int check_shape(int M, int d, int r, int L) {
     return DLRB200_OK;
 }
 
-// Which path serves M rows.  The cluster path handles any M in 128-row tiles
-// once a tile's worth of rows makes the tensor-memory path pay off.
-// Large batches: the cluster kernel (activations resident in tensor memory, the
-// width split over a cluster of d/512 CTAs, one exchange per layer) or the
-// streamed kernel (whole rows per cluster of 1, 2 or 4 CTAs, activations
-// streamed through L2).  Both were timed on a B200 over widths 512..4096, ranks
-// 64 and 128 and 1024..32768 rows; the choice below is a cost model fitted to
-// those times (microseconds):
-//   cluster kernel   waves * L * t_layer, t_layer = 8.2 (r = 128) or 6.4 (r = 64) whatever the width; it
-//                    holds one row tile per cluster, so 8192 rows at d = 4096 are five waves on 15 clusters
-//   streamed kernel  waves * (L + 1) * (chunks per CTA * t_chunk + t_pass), t_chunk = 1.26 (r = 128) or 1.15
-//                    (r = 64), t_pass = 2.5 / 5.5 / 6.8 for a split of 1 / 2 / 4 (normalise + SiLU, and the
-//                    exchange); 30 % more when over 100 unsplit CTAs stream weights that do not fit in L2
-// At d = 4096, r = 128, L = 143: 2048 rows 2.34 ms (cluster) against 2.46 ms, 4096 rows 3.52 against 2.47,
-// 8192 rows 5.89 against 3.77, 16384 rows 10.6 against 7.8, 19200 rows 11.8 against 14.1 (two streamed waves).
-// Shapes the cluster kernel does not cover (d > 4096, d not a multiple of 512, r > d / 32) always stream:
-// 3.7 ms against 27.6 ms on the striped kernel at d = 8192, M = 4096.
+// Which path serves a large batch (M > 64).  Three kernels apply to most shapes:
+//   cluster kernel   activations resident in tensor memory, the width split over a cluster of d/512 CTAs,
+//                    one exchange per layer; holds one 128-row tile per cluster, so 8192 rows at d = 4096 are
+//                    five waves on 15 clusters
+//   streamed kernel  whole rows per cluster of 1, 2 or 4 CTAs, activations streamed through L2
+//   pair kernel      the streamed data flow on CTA pairs (256-row tiles, tcgen05 cta_group::2), two pairs per
+//                    cluster when that still fits the GPU
+// All were timed on a B200 over widths 512..8192, ranks 64 and 128 and 512..32768 rows; the choice is a cost
+// model fitted to those times (microseconds):
+//   cluster   waves * L * t_layer, t_layer = 8.2 (r = 128) or 6.4 (r = 64) whatever the width
+//   streamed  waves * (L + 1) * (chunks per CTA * t_chunk + t_pass), t_chunk = 1.26 (r = 128) or 1.15 (r = 64),
+//             t_pass = 2.5 / 5.5 / 6.8 for a split of 1 / 2 / 4 (normalise + SiLU, and the exchange); 30 % more
+//             when over 100 unsplit CTAs stream weights that do not fit in L2
+//   pairs     waves * (L + 1) * (chunks per pair * t_chunk + t_pass), t_chunk = 1.09 (r = 128) or 0.80 (r = 64),
+//             t_pass = 4.4 with two pairs per cluster (exchange in distributed shared memory), 2.5 with one.
+//             One pair per cluster at rank 128 means at least 9000 rows, where the activations no longer fit in
+//             L2 and the unsplit streamed kernel is as fast or faster: not taken there.
+// At d = 4096, r = 128, L = 143 (ms, cluster / streamed / pairs): 2048 rows 2.34 / 2.47 / 3.09, 4096 rows
+// 3.55 / 2.49 / 3.08, 6144 rows 4.72 / 3.66 / 3.10, 8192 rows 6.37 / 3.86 / 3.14, 16384 rows 12.1 / 7.97 / 8.71.
+// At d = 2048, r = 64, L = 142: 8192 rows 1.82 / 1.98 / 1.51, 16384 rows 3.66 / 2.97 / 2.70.
+// Shapes the cluster kernel does not cover (d > 4096, d not a multiple of 512, r > d / 32) stream.
 struct RouteEntry {
-    int tiles, d, r, L, sms, streamed;     // both plans depend on M only through the number of 128-row tiles
+    int tiles, d, r, L, sms, path;         // the plans depend on M only through the number of 128-row tiles
 };
 constexpr int kRouteSlots = 32;
 RouteEntry g_route[kRouteSlots];
@@ -216,45 +220,71 @@ int g_route_n = 0;          // entries in use
 int g_route_next = 0;       // slot the next new shape goes to (oldest first once the table is full)
 std::mutex g_route_mutex;
 
-bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
+// DLRB200_PATH_* of the kernel that serves M > 64 rows, or 0 when none of the large-batch kernels applies
+// (then the striped kernel runs in 64-row launches).
+int large_batch_path(int M, int d, int r, int L, const DevInfo& di) {
     const int forced = env_int("DLRB200_FORCE_PATH", 0);
-    if (M <= 64 || !dlr::stream_supported(d, r)) return false;
-    if (forced == DLRB200_PATH_STREAMED) return true;
-    if (forced != 0) return false;
-    if (!dlr::cluster_supported(d, r, L)) return true;
+    if (M <= 64) return 0;
+    const bool can_stream = dlr::stream_supported(d, r);
+    const bool can_pair = dlr::stream_pair_supported(d, r);
+    const bool can_cluster = dlr::cluster_supported(d, r, L);
+    if (forced == DLRB200_PATH_STREAMED) return can_stream ? forced : 0;
+    if (forced == DLRB200_PATH_STREAMED_PAIRS) return can_pair ? forced : 0;
+    if (forced == DLRB200_PATH_CLUSTER) return can_cluster ? forced : 0;
+    if (forced != 0) return 0;
+    if (!can_stream && !can_pair) return can_cluster ? DLRB200_PATH_CLUSTER : 0;
     const int tiles = (M + 127) / 128;
-    {   // the two plans below ask the driver for occupancy: remember the answer per shape
+    {   // the plans below ask the driver for occupancy: remember the answer per shape
         std::lock_guard<std::mutex> lock(g_route_mutex);
         for (int i = 0; i < g_route_n; ++i) {
             const RouteEntry& e = g_route[i];
-            if (e.tiles == tiles && e.d == d && e.r == r && e.L == L && e.sms == di.num_sms) return e.streamed != 0;
+            if (e.tiles == tiles && e.d == d && e.r == r && e.L == L && e.sms == di.num_sms) return e.path;
         }
     }
-    dlrb200_plan pc, ps;
-    std::memset(&pc, 0, sizeof(pc));
-    std::memset(&ps, 0, sizeof(ps));
-    if (dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, &pc) != DLRB200_OK) return true;
-    if (dlr::stream_plan(M, d, r, L, di.num_sms, di.smem_optin, &ps) != DLRB200_OK) return false;
-    const double t_cluster = double(pc.passes) * L * (r >= 128 ? 8.2 : 6.4);
-    const double t_pass = ps.cluster >= 4 ? 6.8 : (ps.cluster == 2 ? 5.5 : 2.5);
-    double t_stream = double(ps.passes) * (L + 1) * (double(d / 128 / ps.cluster) * (r >= 128 ? 1.26 : 1.15) + t_pass);
-    if (ps.cluster == 1 && ps.grid > 100 && 4.0 * L * d * r > 100e6) t_stream *= 1.3;
-    const bool streamed = t_stream < 0.97 * t_cluster;
+    double best = 1e30;
+    int path = 0;
+    dlrb200_plan pl;
+    if (can_cluster) {
+        std::memset(&pl, 0, sizeof(pl));
+        if (dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, &pl) == DLRB200_OK) {
+            best = 0.97 * double(pl.passes) * L * (r >= 128 ? 8.2 : 6.4);     // ties go to the cluster kernel
+            path = DLRB200_PATH_CLUSTER;
+        }
+    }
+    if (can_stream) {
+        std::memset(&pl, 0, sizeof(pl));
+        if (dlr::stream_plan(M, d, r, L, di.num_sms, di.smem_optin, &pl) == DLRB200_OK) {
+            const double t_pass = pl.cluster >= 4 ? 6.8 : (pl.cluster == 2 ? 5.5 : 2.5);
+            double t = double(pl.passes) * (L + 1) * (double(d / 128 / pl.cluster) * (r >= 128 ? 1.26 : 1.15) + t_pass);
+            if (pl.cluster == 1 && pl.grid > 100 && 4.0 * L * d * r > 100e6) t *= 1.3;
+            if (t < best) { best = t; path = DLRB200_PATH_STREAMED; }
+        }
+    }
+    if (can_pair) {
+        std::memset(&pl, 0, sizeof(pl));
+        if (dlr::stream_pair_plan(M, d, r, L, di.num_sms, di.smem_optin, &pl) == DLRB200_OK) {
+            const int pp = pl.cluster / 2;
+            // (measured only where the pairs cover most of the GPU: not taken for smaller grids)
+            if ((pp == 2 || r == 64) && pl.grid >= 96) {
+                const double t = double(pl.passes) * (L + 1) *
+                                 (double(d / 128 / pp) * (r >= 128 ? 1.09 : 0.80) + (pp == 2 ? 4.4 : 2.5));
+                if (t < best) { best = t; path = DLRB200_PATH_STREAMED_PAIRS; }
+            }
+        }
+    }
     std::lock_guard<std::mutex> lock(g_route_mutex);
-    g_route[g_route_next] = RouteEntry{tiles, d, r, L, di.num_sms, streamed ? 1 : 0};
+    g_route[g_route_next] = RouteEntry{tiles, d, r, L, di.num_sms, path};
     g_route_next = (g_route_next + 1) % kRouteSlots;
     if (g_route_n < kRouteSlots) ++g_route_n;
-    return streamed;
+    return path;
 }
 
-// The streamed kernel on CTA pairs: same data flow as the streamed kernel, half the weight bytes through each
-// SM's shared memory.
+bool use_stream_path(int M, int d, int r, int L, const DevInfo& di) {
+    return large_batch_path(M, d, r, L, di) == DLRB200_PATH_STREAMED;
+}
+
 bool use_pair_path(int M, int d, int r, int L, const DevInfo& di) {
-    const int forced = env_int("DLRB200_FORCE_PATH", 0);
-    if (M <= 64 || !dlr::stream_pair_supported(d, r)) return false;
-    if (forced == DLRB200_PATH_STREAMED_PAIRS) return true;
-    (void)L; (void)di;
-    return false;
+    return large_batch_path(M, d, r, L, di) == DLRB200_PATH_STREAMED_PAIRS;
 }
 
 bool use_cluster_path(int M, int d, int r, int L) {

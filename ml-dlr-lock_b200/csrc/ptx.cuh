@@ -505,6 +505,17 @@ __device__ __forceinline__ void umma_ts2(uint32_t d_tmem, uint32_t a_tmem, uint6
         : "memory");
 }
 
+// D[tmem, both CTAs] (+)= A[smem of both CTAs: each its own 128 rows] * B[smem halves of both CTAs]; M = 256.
+__device__ __forceinline__ void umma_ss2(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Completion of all tcgen05 work issued so far by this thread arrives on the barrier
 // at this shared-memory offset in every CTA of `cta_mask` (bit = rank in the cluster).
 __device__ __forceinline__ void umma_commit2_mask(uint32_t bar, uint16_t cta_mask) {

@@ -30,7 +30,7 @@ CFG = {  # d, r, L, seed  (the four single-net benchmark configurations)
     "cfg4": (5120, 256, 149, 3),
 }
 
-STRIPED, CLUSTER, CLUSTER_SMALL, STREAMED = 1, 2, 3, 4
+STRIPED, CLUSTER, CLUSTER_SMALL, STREAMED, STREAMED_PAIRS = 1, 2, 3, 4, 5
 
 # (configuration, rows, expected path, expected cluster size or None, expected grid or None)
 CASES = [
@@ -44,7 +44,7 @@ CASES = [
     ("cfg3", 64, None, None, None),
     ("cfg3", 1024, None, None, None),
     ("cfg3", 4096, STREAMED, None, None),
-    ("cfg3", 8192, STREAMED, None, 128),
+    ("cfg3", 8192, STREAMED_PAIRS, 4, 128),
     ("cfg4", 1, STRIPED, 1, 80),
     ("cfg4", 64, STRIPED, 1, 80),
     ("cfg4", 4096, STREAMED, None, None),
@@ -86,7 +86,7 @@ def test_default_routing_at_benchmark_sizes(cfg, M, path, cluster, grid):
     o2 = O.forward_fp32(xs, p)
     e1, e2 = O.rel_l2(ys, o1), O.rel_l2(ys, o2)
     assert e1 <= TOL_TOTAL and e2 <= TOL_TOTAL, (e1, e2)
-    if plan.path in (CLUSTER, STREAMED):
+    if plan.path in (CLUSTER, STREAMED, STREAMED_PAIRS):
         eu = O.rel_l2_update(ys, o1, xs)
         assert eu <= TOL_UPDATE_BF16H, eu
     else:

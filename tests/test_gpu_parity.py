@@ -312,15 +312,20 @@ def test_streamed_path_against_reference_fixtures(D, name, monkeypatch):
 def test_streamed_path_is_chosen_where_it_is_faster_or_alone(D):
     q = D.ops.query
     assert q(1024, 4096, 128, 143).path == 2      # one cluster wave beats a streamed pass over the whole width
-    assert q(8192, 4096, 128, 143).path == 4      # five cluster waves do not beat one streamed wave of 64 pairs
-    assert q(8192, 4096, 128, 143).cluster == 2
+    assert q(8192, 4096, 128, 143).path == 5      # 32 tiles of 256 rows on CTA pairs, two pairs per cluster
+    assert q(8192, 4096, 128, 143).cluster == 4 and q(8192, 4096, 128, 143).grid == 128
+    assert q(6144, 4096, 128, 143).path == 5
+    assert q(4096, 4096, 128, 143).path == 4      # too few 256-row tiles for the pairs: 128-row tiles, clusters of 4
     assert q(4096, 4096, 128, 143).cluster == 4
+    assert q(16384, 4096, 128, 143).path == 4     # one CTA per tile, no exchange at all
     assert q(19200, 4096, 128, 143).path == 2     # two streamed waves lose again
     assert q(4096, 8192, 128, 40).path == 4       # wider than a cluster of 8 can hold
-    assert q(8192, 1536, 64, 40).path == 4        # not a multiple of the cluster kernel's 512-column stripe
+    assert q(8192, 1536, 64, 40).path == 5        # not a multiple of the cluster kernel's 512-column stripe
+    assert q(2048, 1536, 64, 40).path == 4
     assert q(8192, 1024, 32, 141).path == 2       # rank 32 is not streamed
-    assert q(8192, 2048, 64, 142).path == 2
-    assert q(16384, 2048, 64, 142).path == 4
+    assert q(4096, 2048, 64, 142).path == 2
+    assert q(8192, 2048, 64, 142).path == 5
+    assert q(16384, 2048, 64, 142).path == 5
     assert q(8192, 512, 64, 60).path == 2         # a cluster of one CTA has no exchange to lose time in
     assert q(4096, 5120, 256, 149).path == 4      # rank 256: one tensor-memory buffer, still streamed
     assert q(40, 4096, 128, 143).path == 1
@@ -346,6 +351,107 @@ def test_streamed_path_several_tiles_per_cta_and_identity(D, monkeypatch):
     D.ops.check_status()
     assert torch.equal(y0, xx)
     assert O.rel_l2(y[-256:].cpu(), O.forward_fp32(x, p)) <= 1e-2
+
+
+# --------------------------------------------------------------------------- #
+# large-batch streamed path on CTA pairs (256-row tiles, tcgen05 cta_group::2)
+# --------------------------------------------------------------------------- #
+@pytest.mark.parametrize("d,r,L,M,split", [(512, 128, 3, 256, 0), (512, 128, 2, 100, 0), (1024, 128, 5, 300, 1),
+                                           (1024, 128, 5, 300, 2), (2048, 64, 7, 1000, 2), (1536, 64, 4, 257, 0),
+                                           (4096, 128, 3, 129, 0), (640, 128, 3, 65, 0), (1024, 128, 1, 65, 0),
+                                           (2048, 128, 2, 90, 1), (2048, 64, 3, 513, 0), (512, 64, 2, 130, 0)])
+def test_pair_path_shapes(D, d, r, L, M, split, monkeypatch):
+    # ragged row counts (the second CTA of the last pair partly or wholly past the batch), odd chunk counts,
+    # one and two pairs per cluster
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "5")
+    if split:
+        monkeypatch.setenv("DLRB200_PAIR_SPLIT", str(split))
+    p, x = O.seeded_case(d, r, L, M, seed=d + r + M, alpha=1.0, gain_jitter=0.1)
+    plan = D.ops.query(M, d, r, L)
+    assert plan.path == 5 and plan.cluster in (2, 4) and plan.rows_per_pass == 256
+    if split:
+        assert plan.cluster == 2 * split
+    y, Vf, Uf = _run(D, p, x)
+    model = O.forward_folded_fp32(x, Vf, Uf, p.eps, round_h=True)   # activation re-rounded to bf16 after every layer
+    assert O.rel_l2(y, model) <= 6e-3
+    want = O.forward_fp32(x, p)
+    assert O.rel_l2(y, want) <= 1e-2
+    assert O.rel_l2_update(y, want, x) <= 5e-2
+
+
+@pytest.mark.parametrize("name", ["cfg2_d2048_r64", "cfg3_d4096_r128", "toy_d512_r64_stress"])
+@pytest.mark.parametrize("split", [1, 2])
+def test_pair_path_against_reference_fixtures(D, name, split, monkeypatch):
+    g = load_golden(name)
+    m = g["meta"]
+    p, x = O.seeded_case(m["d"], m["r"], m["L"], m["M"], m["seed"], m["alpha"], m["gain_jitter"])
+    reps = 300 // m["M"] + 1                     # more than one 256-row tile: repeat the fixture rows
+    xx = x.repeat(reps, 1)
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "5")
+    monkeypatch.setenv("DLRB200_PAIR_SPLIT", str(split))
+    if split == 2 and m["d"] < 1024:
+        pytest.skip("two pairs per cluster need at least eight chunks")
+    assert D.ops.query(xx.shape[0], m["d"], m["r"], m["L"]).path == 5
+    y, Vf, Uf = _run(D, p, xx)
+    for k in range(reps):                        # rows are independent: every copy gives the fixture's answer
+        assert torch.equal(y[k * m["M"]:(k + 1) * m["M"]], y[:m["M"]])
+    y = y[:m["M"]]
+    assert O.rel_l2(y, g["y_bf16"]) <= (TOL_TOTAL if m["alpha"] < 0.5 else 2.5e-2)
+    assert O.rel_l2(y, g["y_fp32"]) <= TOL_TOTAL
+    assert O.rel_l2_update(y, g["y_bf16"], x) <= 0.3
+
+
+def test_pair_path_several_tiles_per_cluster_identity_and_graph_replay(D, monkeypatch):
+    # more 256-row tiles than clusters fit: clusters walk several tiles; alpha = 0 returns the input bit for
+    # bit; a captured launch replays to the same bits as a direct call
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "5")
+    d, r, L, M = 512, 64, 3, 256 * 80 + 37
+    dev = torch.device("cuda:0")
+    p, x = O.seeded_case(d, r, L, 256, seed=11, alpha=1.0, gain_jitter=0.1)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    xx = torch.randn(M, d, device=dev, generator=gen).to(torch.bfloat16)
+    xx[-256:] = x.to(dev)
+    assert D.ops.query(M, d, r, L).passes == 2
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    y = D.ops.forward_folded(xx, Vf, Uf)
+    Vz, Uz = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), torch.zeros(L, device=dev))
+    y0 = D.ops.forward_folded(xx, Vz, Uz)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert torch.equal(y0, xx)
+    assert O.rel_l2(y[-256:].cpu(), O.forward_fp32(x, p)) <= 1e-2
+    out = torch.empty_like(xx)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        D.ops.forward_folded(xx, Vf, Uf, out=out)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        D.ops.forward_folded(xx, Vf, Uf, out=out)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert torch.equal(out, y)
+
+
+def test_pair_path_reports_a_timeout_instead_of_hanging(D, monkeypatch):
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "5")
+    p, x = O.seeded_case(1024, 128, 4, 600, seed=9, alpha=1.0, gain_jitter=0.1)
+    dev = torch.device("cuda:0")
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    monkeypatch.setenv("DLRB200_SPIN_LIMIT", "4")
+    D.ops.forward_folded(x.to(dev), Vf, Uf)
+    torch.cuda.synchronize()
+    with pytest.raises(D.ops._lib.DlrB200Error):
+        D.ops.check_status()
+    monkeypatch.delenv("DLRB200_SPIN_LIMIT")
+    y = D.ops.forward_folded(x.to(dev), Vf, Uf)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert O.rel_l2(y.cpu(), O.forward_fp32(x, p)) <= 1e-2
 
 
 def test_streamed_path_reports_a_timeout_instead_of_hanging(D, monkeypatch):
