@@ -217,7 +217,7 @@ def torch_loop_same_box(x, Vp, Up, eps=1e-6):
     return {"ms_per_step": ms, "tokens_per_s": x.shape[0] / (ms * 1e-3), "what": "eager torch bf16 layer loop on folded weights, same GPU, same input"}
 
 
-def locked_decoder_loop(dev, batch=8, prompt=512, steps=256, eager_steps=2):
+def locked_decoder_loop(dev, batch=8, prompt=512, steps=256, eager_steps=2, fused=True):
     """The locked decoder loop on synthetic shapes: a randomly initialised Qwen3-shaped decoder (28 layers,
     hidden 1024, 16 query / 8 key-value heads of 128, d_ff 3072, vocabulary 151936) whose MLPs are DLR-Nets of
     rank 32 (depth 141), batch 8, 512 uniform-random prompt ids, 256 greedy steps on the KV cache.  Timed with
@@ -282,6 +282,8 @@ def locked_decoder_loop(dev, batch=8, prompt=512, steps=256, eager_steps=2):
             return (time.perf_counter() - t0) * 1e3 / n_steps
 
     D.set_fast_path(model, True)
+    if fused:
+        D.fuse_decoder_layers(model)          # the net's output is the layer's output: no "- h" / "+ h" passes
     run(2)                                    # warm-up: weights folded, workspaces allocated
     pre_ms, step_ms = run(32)
     try:
@@ -290,18 +292,46 @@ def locked_decoder_loop(dev, batch=8, prompt=512, steps=256, eager_steps=2):
     except Exception as e:                    # host framework without a capturable static cache
         graph_ms, graph_note = None, f"not captured: {type(e).__name__}"
     D.ops.check_status()
-    D.set_fast_path(model, False)
-    run(1)
-    pre_eager, step_eager = run(eager_steps)
+    torch_loop = None
+    if eager_steps > 0:
+        D.set_fast_path(model, False)
+        if fused:
+            D.fuse_decoder_layers(model, False)
+        run(1)
+        pre_eager, step_eager = run(eager_steps)
+        torch_loop = {"prefill_ms": pre_eager, "decode_ms_per_step": step_eager, "steps_timed": eager_steps}
     del model
     torch.cuda.empty_cache()
     best = graph_ms if graph_ms is not None else step_ms
-    return {"config": f"qwen3-shaped random init, 28 layers, d=1024, r=32, L=141, batch {batch}, prompt {prompt}, {steps} greedy steps",
+    return {"batch": batch, "fused_residual": bool(fused), "config": f"qwen3-shaped random init, 28 layers, d=1024, r=32, L=141, batch {batch}, prompt {prompt}, {steps} greedy steps",
             "prefill_ms": pre_ms, "prefill_tokens_per_s": batch * prompt / (pre_ms * 1e-3),
             "decode_ms_per_step": best, "decode_tokens_per_s": batch / (best * 1e-3),
             "decode_mode": graph_note, "decode_ms_per_step_plain_loop": step_ms,
-            "torch_loop": {"prefill_ms": pre_eager, "decode_ms_per_step": step_eager, "steps_timed": eager_steps},
+            "torch_loop": torch_loop,
             "timing": "host clock around synchronised regions (the loop includes the host framework's attention and sampling)"}
+
+
+def cpu_baseline_cfg1(rows=2048, budget_s=8.0):
+    """The stated CPU baseline configuration: d=1024, r=32, L=141, M=2048 rows, seed 0, the reference's
+    torch loop (oracle port) in fp32 and in bf16 on this machine's cores, best of up to 5 after one warm-up."""
+    from oracle import dlrnet_oracle as O
+    n = os.cpu_count() or 1
+    if torch.get_num_threads() < n:
+        torch.set_num_threads(min(n, 64))
+    d, _, r, L, seed = WORKLOADS["cfg1"]
+    p, x = O.seeded_case(d, r, L, rows, seed, alpha=0.01)
+    out = {"config": f"cfg1: d={d} r={r} L={L}, M={rows} rows, seed {seed}", "cores": torch.get_num_threads(),
+           "nproc": n, "kind": "port"}
+    for name, fn in (("fp32", lambda: O.forward_fp32(x, p)), ("bf16", lambda: O.forward_eager(x, p))):
+        fn()
+        best, spent, reps = float("inf"), 0.0, 0
+        while spent < budget_s / 2 and reps < 5:
+            t0 = time.perf_counter()
+            fn()
+            dt = time.perf_counter() - t0
+            best, spent, reps = min(best, dt), spent + dt, reps + 1
+        out[name] = {"seconds": best, "tokens_per_s": rows / best, "best_of": reps}
+    return out
 
 
 def cpu_baseline(d, r, L, seed, rows=512, budget_s=12.0):
@@ -367,6 +397,155 @@ def emit(line):
         print(json.dumps(line), flush=True)
 
 
+def _max_over_ranks(vals, dev, world):
+    if world == 1:
+        return [float(v) for v in vals]
+    import torch.distributed as dist
+    t = torch.tensor(list(vals), device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def sharded_block(dev, world, rank, barrier, Vp, Up, d, r, L, steps):
+    """ONE batch of M rows split over the ranks in contiguous row blocks (weights replicated, rows are
+    independent: dlr_lock/model.py:93-101 has no cross-row op), forward per rank, one all-gather of the output
+    blocks.  Reported per M: time of the single-GPU forward of the whole batch (every rank measures it on its own
+    GPU: the N = 1 reference of the strong-scaling figure), time of the sharded forward alone and with the gather
+    inside the timed region (device time, maximum over ranks), and that the gathered output equals the single-GPU
+    output bit for bit."""
+    from dlr_lock_b200 import ops, sharding
+    fwd = sharding.RowShardedForward(lambda x: ops.forward_folded(x, Vp, Up), tile=128)
+    out = []
+    for M in (8192, 4096, 1024):
+        g = torch.Generator(device=dev)
+        g.manual_seed(4242 + M)                         # same batch on every rank
+        x = torch.randn(M, d, device=dev, generator=g).to(torch.bfloat16)
+        y_full = ops.forward_folded(x, Vp, Up)
+        a, b = fwd.local_rows(M)
+        xl = x[a:b].contiguous()
+        y_all = fwd.gather(ops.forward_folded(xl, Vp, Up), M) if b > a or world > 1 else y_full
+        torch.cuda.synchronize()
+        same = bool(torch.equal(y_all, y_full))
+        n = max(3, min(steps, 10))
+        t_full = time_steps(lambda: ops.forward_folded(x, Vp, Up), n, 3, barrier) / n
+        t_local = time_steps(lambda: ops.forward_folded(xl, Vp, Up), n, 3, barrier) / n
+        t_gather = time_steps(lambda: fwd.gather(ops.forward_folded(xl, Vp, Up), M), n, 3, barrier) / n
+        t_full, t_local, t_gather = _max_over_ranks([t_full, t_local, t_gather], dev, world)
+        plan = ops.query(max(b - a, 1), d, r, L)
+        out.append({"M": M, "rows_per_gpu": b - a, "ms_single_gpu_whole_batch": t_full, "ms_sharded_forward": t_local,
+                    "ms_sharded_forward_and_gather": t_gather, "tokens_per_s_no_gather": M / (t_local * 1e-3),
+                    "tokens_per_s_with_gather": M / (t_gather * 1e-3),
+                    "strong_scaling_efficiency_no_gather": t_full / (world * t_local),
+                    "strong_scaling_efficiency_with_gather": t_full / (world * t_gather),
+                    "gathered_equals_single_gpu_bits": same,
+                    "per_gpu_plan": {"path": plan.path, "grid": plan.grid, "cluster": plan.cluster, "passes": plan.passes}})
+        del x, y_full, y_all, xl
+    ops.check_status()
+    return {"what": "one batch split in contiguous row blocks, final all_gather_into_tensor (NCCL)", "n_gpus": world, "cases": out,
+            "limit": "at 1024 rows per GPU the cluster kernel runs one wave of row tiles on part of the SMs: the per-GPU time "
+                     "stops falling with the row count, which bounds strong scaling; the gather itself is NVLink-bound"}
+
+
+def decode_sweep(dev, name, Ms, peaks):
+    from dlr_lock_b200 import ops
+    d, _, r, L, seed = WORKLOADS[name]
+    Vp, Up = make_weights(d, r, L, seed, dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(77 + seed)
+    x = torch.randn(max(Ms), d, device=dev, generator=g).to(torch.bfloat16)
+    wbytes = 4.0 * L * d * r
+    rows = []
+    for m in Ms:
+        xm, ym = x[:m].contiguous(), torch.empty(m, d, device=dev, dtype=torch.bfloat16)
+        plan = ops.query(m, d, r, L)
+        if m <= 64:
+            lo, med = min_latency_us(lambda: ops.forward_folded(xm, Vp, Up, out=ym))
+            gbs = (wbytes + 4.0 * m * d) / (lo * 1e-6) / 1e9
+            rows.append({"M": m, "path": plan.path, "min_us": lo, "median_us": med, "us_per_layer": lo / L,
+                         "algorithmic_GBps": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "tokens_per_s": m / (lo * 1e-6)})
+        else:
+            lo, med = min_latency_us(lambda: ops.forward_folded(xm, Vp, Up, out=ym), iters=10, warmup=3)
+            tf = 4.0 * L * m * d * r / (lo * 1e-6) / 1e12
+            rows.append({"M": m, "path": plan.path, "cluster": plan.cluster, "grid": plan.grid, "min_us": lo,
+                         "tokens_per_s": m / (lo * 1e-6), "TFLOPs": tf, "frac_of_measured_bf16_burst": tf / peaks["tf_burst"]})
+    ops.check_status()
+    del Vp, Up, x
+    torch.cuda.empty_cache()
+    return {"config": f"{name}: d={d} r={r} L={L}", "weights_MB": wbytes / 1e6, "cases": rows}
+
+
+def same_box_comparisons(dev, x, Vp, Up, d, r, L, seed, workload, rows):
+    """Library-only ways of running the same stack on this GPU (comparison figures; nothing of the product path):
+    the eager torch loop, the cuBLAS + elementwise loop captured in one CUDA graph (the form of
+    kernels/kernels/orchestrated.py:95-126) and the torch module under torch.compile(mode="reduce-overhead")
+    (kernels/bench/bench_paper.py:178), the last in a child process with a time limit."""
+    import subprocess
+    from dlr_lock_b200 import harness
+    out = {"eager_torch_loop": torch_loop_same_box(x, Vp, Up)}
+    try:
+        weights = {"Vs": Vp.transpose(1, 2).contiguous(), "Us": Up.transpose(1, 2).contiguous(), "L": L, "D": d, "R": r,
+                   "premultiplied": True}
+        graph, hbuf = harness.orchestrated_graph(x, weights)
+        graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / 3
+        out["cublas_graph_loop"] = {"ms_per_step": ms, "tokens_per_s": x.shape[0] / (ms * 1e-3),
+                                    "what": "per layer cuBLAS GEMM, elementwise rstd*SiLU, cuBLAS addmm_; one CUDA graph"}
+        del graph, hbuf, weights
+    except Exception as e:  # noqa: BLE001
+        out["cublas_graph_loop"] = {"status": f"{type(e).__name__}: {e}"[:200]}
+    torch.cuda.empty_cache()
+    try:
+        cmd = [sys.executable, os.path.abspath(__file__), "--compare-child", "compile", "--workload", workload, "--rows", str(rows)]
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
+        line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+        out["torch_compile_reduce_overhead"] = json.loads(line[-1]) if line else {"status": "no output", "stderr": res.stderr[-300:]}
+    except subprocess.TimeoutExpired:
+        out["torch_compile_reduce_overhead"] = {"status": "not finished within 240 s (compilation of the unrolled stack)"}
+    except Exception as e:  # noqa: BLE001
+        out["torch_compile_reduce_overhead"] = {"status": f"{type(e).__name__}: {e}"[:200]}
+    out["triton_fused"] = {"status": "not run: the reference's Triton source is not on this machine and is not reproduced here"}
+    return out
+
+
+def compare_child(args):
+    """Child process of same_box_comparisons: the torch module of the workload under
+    torch.compile(mode="reduce-overhead")."""
+    import dlr_lock_b200 as D
+    from dlr_lock_b200 import harness
+    d, _, r, L, seed = WORKLOADS[args.workload]
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(seed)
+    net = D.DLRNet(d, r, L, alpha_init=0.01).to(torch.bfloat16).to(dev).eval()
+    for p in net.parameters():
+        p.requires_grad_(False)
+    x = torch.randn(args.rows, d, device=dev).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    fn = harness.compiled_reduce_overhead(net)
+    with torch.no_grad():
+        for _ in range(3):
+            y = fn(x)
+        torch.cuda.synchronize()
+        compile_s = time.perf_counter() - t0
+        net.fast = False
+        err = harness.rel_err(y, net(x))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            fn(x)
+        b.record()
+        torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 3
+    print(json.dumps({"ms_per_step": ms, "tokens_per_s": args.rows / (ms * 1e-3), "compile_s": compile_s,
+                      "rel_err_vs_eager": err, "what": "torch.compile(mode='reduce-overhead') of the eager module"}), flush=True)
+
+
 def main():
     quiet_stdout()
     ap = argparse.ArgumentParser()
@@ -376,11 +555,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
     ap.add_argument("--rows", type=int, default=8192, help="token rows per GPU per step")
-    ap.add_argument("--no-extras", action="store_true", help="skip decode sweep, e2e and CPU baseline")
+    ap.add_argument("--no-extras", action="store_true", help="headline only: skip e2e, sharding, decode sweeps, comparisons, CPU baseline")
+    ap.add_argument("--compare-child", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     d, d_ff, r, L, seed = WORKLOADS[args.workload]
 
+    if args.compare_child:
+        global _REAL_STDOUT
+        os.dup2(_REAL_STDOUT, 1)
+        _REAL_STDOUT = None
+        compare_child(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args, d, r, L, seed)
         return
@@ -423,31 +609,37 @@ def main():
     ms = time_steps(step, args.steps, args.warmup, barrier)
     clocks = sampler.stop()
     ops.check_status()
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    (ms,) = _max_over_ranks([ms], dev, world)
     ms_step = ms / args.steps
     value = world * M * 1e3 / ms_step
 
-    flops = 4.0 * L * M * d * r
+    path_name = {1: "striped", 2: "cluster", 3: "cluster_small", 4: "streamed", 5: "streamed_pairs"}.get(plan.path, "?")
     launches_per_step = plan.passes if plan.path == 1 else 1   # the striped path launches once per 64 rows
     kernel_ms = ms_step / launches_per_step
     timed_s = ms / 1e3
-    peak_tf = peaks["tf_sustained"] if timed_s > 1.0 else peaks["tf_burst"]
-    achieved_tf = flops / launches_per_step / (kernel_ms * 1e-3) / 1e12
-    # DRAM traffic per launch: one ncu capture of a one-wave launch (profiles/) showed traffic equal to the
-    # algorithmic bytes; weights exceed L2, so a launch of several waves re-reads them once per wave.
-    tiles = (M + 127) // 128
-    waves = plan.passes          # cluster / streamed paths: waves of row tiles inside the one launch
-    traffic = waves * 4.0 * L * d * r + 4.0 * M * d
-    roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
-                "frac": achieved_tf / peak_tf, "traffic": traffic,
-                "traffic_note": "bytes per launch, scaled by waves from a one-wave ncu capture",
-                "peak_source": f"{peaks['source']} ({'sustained' if timed_s > 1.0 else 'burst'})",
-                "kernel": {1: "striped", 2: "cluster", 3: "cluster_small", 4: "streamed"}.get(plan.path, "?"), "kernel_ms": kernel_ms,
-                "frac_of_nominal_2250": achieved_tf / 2250.0}
+    if plan.path in (1, 3):
+        # small-batch kernels stream the weights once per launch: HBM-bound by design
+        bytes_alg = 4.0 * L * d * r + 4.0 * min(M, 64) * d
+        achieved = bytes_alg / (kernel_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": bytes_alg,
+                    "traffic_note": "ncu capture of the striped kernel (profiles/): DRAM bytes equal the algorithmic bytes",
+                    "peak_source": f"{peaks['source']} (copy bandwidth)", "kernel": path_name, "kernel_ms": kernel_ms}
+    else:
+        flops = 4.0 * L * M * d * r
+        peak_tf = peaks["tf_sustained"] if timed_s > 1.0 else peaks["tf_burst"]
+        achieved_tf = flops / launches_per_step / (kernel_ms * 1e-3) / 1e12
+        alg_bytes = 4.0 * L * d * r + 4.0 * M * d
+        if args.workload == "cfg3" and M == 8192 and plan.path == 5:
+            # one ncu capture of this very launch (profiles/streamed_pairs_kernel_cfg3_M8192.md)
+            traffic, note = 1.057e9 + 1.574e9, ("measured: dram__bytes_read + dram__bytes_write of one captured launch of this "
+                                                "configuration; the activations (134 MB through L2 per layer) do not stay in L2 entirely")
+        else:
+            traffic, note = plan.passes * 4.0 * L * d * r + 4.0 * M * d, "not captured at this size: waves x weights + activations"
+        roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
+                    "frac": achieved_tf / peak_tf, "traffic": traffic, "traffic_note": note, "algorithmic_bytes": alg_bytes,
+                    "peak_source": f"{peaks['source']} ({'sustained' if timed_s > 1.0 else 'burst'})",
+                    "kernel": path_name, "kernel_ms": kernel_ms, "frac_of_nominal_2250": achieved_tf / 2250.0}
 
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -461,6 +653,21 @@ def main():
         "plan": {"path": plan.path, "grid": plan.grid, "cluster": plan.cluster, "stripe_cols": plan.stripe_cols,
                  "passes": plan.passes},
     }
+
+    # ---- the same step for at least two seconds: what the kernel sustains under the power cap
+    if not args.no_extras and plan.path not in (1, 3):
+        n_long = int(math.ceil(2200.0 / ms_step))
+        s2 = ClockSampler(local)
+        s2.start()
+        s2.mark()
+        ms_long = time_steps(step, n_long, 3, barrier)
+        clk = s2.stop()
+        (ms_long,) = _max_over_ranks([ms_long], dev, world)
+        tf = 4.0 * L * M * d * r / (ms_long / n_long * 1e-3) / 1e12
+        line["sustained"] = {"steps": n_long, "seconds": ms_long / 1e3, "ms_per_step": ms_long / n_long,
+                             "tokens_per_s": world * M * n_long * 1e3 / ms_long, "TFLOPs_per_gpu": tf,
+                             "frac_of_measured_sustained_bf16": tf / peaks["tf_sustained"], "clocks": clk}
+        ops.check_status()
 
     # ---- end to end through the host-buffer entry point (every rank, max over ranks)
     if not args.no_extras:
@@ -503,18 +710,43 @@ def main():
         if barrier:
             barrier()
         ms_h = ea.elapsed_time(eb)
-        if world > 1:
-            t = torch.tensor([ms_h, ms_serial], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_h, ms_serial = float(t[0].item()), float(t[1].item())
+        ms_h, ms_serial = _max_over_ranks([ms_h, ms_serial], dev, world)
         line["e2e"] = {"value": world * M * args.steps * 1e3 / ms_h, "unit": "tokens/s",
                        "h2d_bytes_per_step": M * d * 2, "d2h_bytes_per_step": M * d * 2,
                        "ms_per_step": ms_h / args.steps,
                        "mode": "dlrb200_forward_host from pinned host buffers, steps alternating between two streams",
                        "one_stream": {"value": world * M * args.steps * 1e3 / ms_serial, "ms_per_step": ms_serial / args.steps}}
         ops.check_status()
+        del xh, yh
 
-    # ---- small-batch latencies and other prefill sizes (rank 0, N=1 only)
+    # ---- one batch sharded by rows over the ranks, with the final gather (every N; at N = 1 it is the reference point)
+    if not args.no_extras and args.workload == "cfg3":
+        line["sharded"] = sharded_block(dev, world, rank, barrier, Vp, Up, d, r, L, args.steps)
+
+    # ---- the locked decoder loop over N GPUs, batch-sharded: the sequences of a batch are independent, every rank
+    # runs its own sequences on its own replica of the model and KV cache, no collective in the loop
+    if not args.no_extras and args.workload == "cfg3":
+        if world == 1:
+            line["locked_decoder"] = locked_decoder_loop(dev)
+        else:
+            steps_n = 64
+            strong_b = max(1, 8 // world)
+            strong = locked_decoder_loop(dev, batch=strong_b, steps=steps_n, eager_steps=0) if world <= 8 else None
+            weak = locked_decoder_loop(dev, batch=8, steps=steps_n, eager_steps=0)
+            vals = _max_over_ranks([strong["decode_ms_per_step"], strong["prefill_ms"], weak["decode_ms_per_step"], weak["prefill_ms"]],
+                                   dev, world)
+            line["locked_decoder"] = {
+                "config": strong["config"].split(", batch")[0] + f", prompt 512, {steps_n} greedy steps, {world} GPUs, batch-sharded",
+                "strong": {"batch_total": strong_b * world, "batch_per_gpu": strong_b, "decode_ms_per_step": vals[0], "prefill_ms": vals[1],
+                           "decode_tokens_per_s": strong_b * world / (vals[0] * 1e-3),
+                           "prefill_tokens_per_s": strong_b * world * 512 / (vals[1] * 1e-3)},
+                "weak": {"batch_total": 8 * world, "batch_per_gpu": 8, "decode_ms_per_step": vals[2], "prefill_ms": vals[3],
+                         "decode_tokens_per_s": 8 * world / (vals[2] * 1e-3),
+                         "prefill_tokens_per_s": 8 * world * 512 / (vals[3] * 1e-3)},
+                "decode_mode": weak["decode_mode"], "fused_residual": weak["fused_residual"],
+                "timing": "host clock around synchronised regions, maximum over ranks"}
+
+    # ---- small-batch latencies, other sizes and shapes, comparisons, CPU baselines (rank 0, N=1 only)
     if not args.no_extras and world == 1:
         wbytes = 4.0 * L * d * r
         dec = []
@@ -522,8 +754,8 @@ def main():
             xm, ym = xs[0][:m].contiguous(), torch.empty(m, d, device=dev, dtype=torch.bfloat16)
             lo, med = min_latency_us(lambda: ops.forward_folded(xm, Vp, Up, out=ym))
             gbs = (wbytes + 4.0 * m * d) / (lo * 1e-6) / 1e9
-            dec.append({"M": m, "min_us": lo, "median_us": med, "us_per_layer": lo / L, "algorithmic_GBps": gbs,
-                        "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "tokens_per_s": m / (lo * 1e-6)})
+            dec.append({"M": m, "path": ops.query(m, d, r, L).path, "min_us": lo, "median_us": med, "us_per_layer": lo / L,
+                        "algorithmic_GBps": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "tokens_per_s": m / (lo * 1e-6)})
         line["decode"] = dec
         pre = []
         for m in (1024, 4096):
@@ -531,18 +763,27 @@ def main():
                 continue
             xm, ym = xs[0][:m].contiguous(), torch.empty(m, d, device=dev, dtype=torch.bfloat16)
             lo, med = min_latency_us(lambda: ops.forward_folded(xm, Vp, Up, out=ym), iters=10, warmup=3)
-            pre.append({"M": m, "min_us": lo, "tokens_per_s": m / (lo * 1e-6),
+            pre.append({"M": m, "path": ops.query(m, d, r, L).path, "min_us": lo, "tokens_per_s": m / (lo * 1e-6),
                         "TFLOPs": 4.0 * L * m * d * r / (lo * 1e-6) / 1e12})
         line["prefill_other"] = pre
         ops.check_status()
-        line["same_box_torch_loop"] = torch_loop_same_box(xs[0], Vp, Up)
+        line["same_box"] = same_box_comparisons(dev, xs[0], Vp, Up, d, r, L, seed, args.workload, M)
+        line["same_box_torch_loop"] = line["same_box"]["eager_torch_loop"]
+        del xs, ys, Vp, Up
+        torch.cuda.empty_cache()
         if args.workload == "cfg3":
-            line["locked_decoder"] = locked_decoder_loop(dev)
+            line["other_configs"] = {
+                "cfg1": decode_sweep(dev, "cfg1", (1, 16, 64, 2048), peaks),
+                "cfg2": decode_sweep(dev, "cfg2", (1, 4, 16, 64, 8192), peaks),
+                "cfg4": decode_sweep(dev, "cfg4", (1, 64, 4096), peaks),
+            }
+            line["cpu_baseline_cfg1"] = cpu_baseline_cfg1()
         line["cpu_baseline"] = cpu_baseline(d, r, L, seed)
 
     if rank == 0:
         emit(line)
     if world > 1:
+        import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
 

@@ -236,6 +236,10 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             // the weight stages of both CTAs are counted on the leader's barriers
             const uint32_t ufull_lead = mapa(smem_u32(&bars->u_full[0]), lead);
             const uint32_t vfull_lead = mapa(smem_u32(&bars->v_full[0]), lead);
+            // the weights pass through L2 once per cluster and layer, the activations come back every layer: tell
+            // L2 which to keep (without the hints over half of every layer's output is written back to DRAM)
+            const uint64_t pol_w = l2_policy_evict_first(), pol_h = l2_policy_evict_last();
+            const bool hints = !(PROF && (p.exp & 32));
             while ((nu < total_w || nv < total_w || nh < total_h) && !err) {
                 bool did = false;
                 // pass >= 1 reads what this CTA stored one pass (nch chunks) earlier
@@ -248,8 +252,14 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     const int m0 = (cl + ht * ncl) * 2 * kRowsP + hf * kRowsP;
                     DLP_T(0, hq, hc, 0);
                     mbar_arrive_expect_tx(bar, kHBytesP);
-                    tma_load_2d(dst, src, col0 + hc * kCWP, m0, bar);
-                    tma_load_2d(dst + 16384, src, col0 + hc * kCWP + 64, m0, bar);
+                    if (hints) {
+                        const uint64_t pol = hq >= 1 ? pol_h : pol_w;      // x is read once
+                        tma_load_2d_hint(dst, src, col0 + hc * kCWP, m0, bar, pol);
+                        tma_load_2d_hint(dst + 16384, src, col0 + hc * kCWP + 64, m0, bar, pol);
+                    } else {
+                        tma_load_2d(dst, src, col0 + hc * kCWP, m0, bar);
+                        tma_load_2d(dst + 16384, src, col0 + hc * kCWP + 64, m0, bar);
+                    }
                     hph[hp.st] = int(hp.ph);
                     hp.step(kNLP);
                     ++nh;
@@ -262,8 +272,12 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     if (hf == 0) mbar_arrive_expect_tx(smem_u32(&bars->u_full[up.st]), 2 * C::U_BYTES);
 #pragma unroll
                     for (int t = 0; t < C::UT; ++t)
-                        tma_load_2d_pair(dst + t * C::U_TILE_BYTES, &tmU, 64 * t, uq * p.d + col0 + uc * kCWP + 64 * hf,
-                                         ufull_lead + 8u * up.st);
+                        if (hints)
+                            tma_load_2d_pair_hint(dst + t * C::U_TILE_BYTES, &tmU, 64 * t, uq * p.d + col0 + uc * kCWP + 64 * hf,
+                                                  ufull_lead + 8u * up.st, pol_w);
+                        else
+                            tma_load_2d_pair(dst + t * C::U_TILE_BYTES, &tmU, 64 * t, uq * p.d + col0 + uc * kCWP + 64 * hf,
+                                             ufull_lead + 8u * up.st);
                     uph[up.st] = int(up.ph);
                     up.step(NU);
                     ++nu;
@@ -276,8 +290,12 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     if (hf == 0) mbar_arrive_expect_tx(smem_u32(&bars->v_full[vp.st]), 2 * C::V_BYTES);
 #pragma unroll
                     for (int t = 0; t < 2; ++t)
-                        tma_load_2d_pair(dst + t * C::V_TILE_BYTES, &tmV, col0 + vc * kCWP + 64 * t, vq * R + (R / 2) * hf,
-                                         vfull_lead + 8u * vp.st);
+                        if (hints)
+                            tma_load_2d_pair_hint(dst + t * C::V_TILE_BYTES, &tmV, col0 + vc * kCWP + 64 * t, vq * R + (R / 2) * hf,
+                                                  vfull_lead + 8u * vp.st, pol_w);
+                        else
+                            tma_load_2d_pair(dst + t * C::V_TILE_BYTES, &tmV, col0 + vc * kCWP + 64 * t, vq * R + (R / 2) * hf,
+                                             vfull_lead + 8u * vp.st);
                     vph[vp.st] = int(vp.ph);
                     vp.step(NV);
                     ++nv;
@@ -395,6 +413,8 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
         // so that this warp never waits for a write in flight.
         if (lane == 0) {
             RingPos sp;
+            const uint64_t pol_h = l2_policy_evict_last();
+            const bool hints = !(PROF && (p.exp & 32));
             unsigned int n = 0;              // chunks seen (all tiles, all passes): the producer counts the same way
             for (int t = 0; t < my_tiles && !err; ++t) {
                 const int m0 = (cl + t * ncl) * 2 * kRowsP + hf * kRowsP;
@@ -409,8 +429,13 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                         DLP_T(5, q, c, 0);
                         if (m0 < p.M && !(PROF && (p.exp & 8))) {   // a CTA whose rows lie wholly past the batch stores nothing
                             const uint32_t src = sbuf_s + sp.st * kHBytesP;
-                            tma_store_2d(&tmY, col0 + c * kCWP, m0, src);
-                            tma_store_2d(&tmY, col0 + c * kCWP + 64, m0, src + 16384);
+                            if (hints && q + 1 < p.L) {       // the last layer's output is not read again here
+                                tma_store_2d_hint(&tmY, col0 + c * kCWP, m0, src, pol_h);
+                                tma_store_2d_hint(&tmY, col0 + c * kCWP + 64, m0, src + 16384, pol_h);
+                            } else {
+                                tma_store_2d(&tmY, col0 + c * kCWP, m0, src);
+                                tma_store_2d(&tmY, col0 + c * kCWP + 64, m0, src + 16384);
+                            }
                         }
                         bulk_commit_group();
                         bulk_wait_group_read<0>();

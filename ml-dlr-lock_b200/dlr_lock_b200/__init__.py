@@ -12,6 +12,7 @@ from .model import (  # noqa: F401
     compute_depth,
     dlrnet_config,
     dlrnet_param_count,
+    fuse_decoder_layers,
     load_dlrnet_weights,
     locked_model_from_config,
     replace_layer_mlp,
@@ -20,7 +21,7 @@ from .model import (  # noqa: F401
     set_fast_path,
     write_config,
 )
-from . import ops, packed, registry, sharding  # noqa: F401
+from . import harness, ops, packed, registry, sharding  # noqa: F401
 from .packed import PackedNet, load_packed_weights, pack_state_dict  # noqa: F401
 
 __version__ = "0.1.0"

@@ -283,14 +283,55 @@ def set_checkpointing(model, enabled):
     return n
 
 
-def accelerate_locked_model(model) -> int:
+def _fused_locked_layer_forward(self, hidden_states, **kwargs):
+    """A locked pre-norm decoder layer with the MLP branch's residual arithmetic cancelled.
+
+    The host framework computes ``h = x + attn(norm(x))`` and then ``h + mlp(post_norm(h))``; in a locked
+    layer ``post_norm`` is the identity and ``mlp`` is ``ResidualDLRNet``, i.e. ``dlrnet(h) - h``
+    (dlr_lock/model.py:104-122, 174-175), so the layer's output is ``dlrnet(h)``.  Here the attention
+    output goes straight into the net and the net's output is the layer's output: the ``- h`` and the
+    ``+ h`` (two passes over the activations and two launches per layer) never run.  Arguments are passed
+    through to the layer's own attention module unchanged.
+    """
+    attn = self.self_attn(hidden_states=self.input_layernorm(hidden_states), **kwargs)
+    if isinstance(attn, tuple):
+        attn = attn[0]
+    return self.mlp.dlrnet(hidden_states + attn)
+
+
+def _fusable(layer) -> bool:
+    return (isinstance(getattr(layer, "mlp", None), ResidualDLRNet)
+            and isinstance(getattr(layer, "post_attention_layernorm", None), nn.Identity)
+            and hasattr(layer, "input_layernorm") and hasattr(layer, "self_attn"))
+
+
+def fuse_decoder_layers(model, enabled: bool = True) -> int:
+    """Switch every locked decoder layer of ``model`` between the host framework's own forward (the
+    reference composition ``h + (dlrnet(h) - h)``) and the fused one (``dlrnet(h)``).  Only layers of the
+    standard pre-norm form are touched (``input_layernorm``, ``self_attn``, an identity
+    ``post_attention_layernorm`` and a ``ResidualDLRNet`` as ``mlp``).  Returns how many were switched."""
+    import types
+    n = 0
+    for layer in model.model.layers:
+        if not _fusable(layer):
+            continue
+        if enabled:
+            layer.forward = types.MethodType(_fused_locked_layer_forward, layer)
+        elif "forward" in layer.__dict__:
+            del layer.__dict__["forward"]
+        n += 1
+    return n
+
+
+def accelerate_locked_model(model, fuse_layers: bool = False) -> int:
     """Route every DLR-Net of a locked model through the B200 library.
 
     Works on models built by this package or by the reference's
     ``build_locked_model``: each ``layers[i].mlp.dlrnet`` that is not already a
     :class:`DLRNet` of this package is replaced by one that shares its
     parameters, so ``load_dlrnet_weights`` / ``save_dlrnet_weights`` /
-    ``set_checkpointing`` keep working.  Returns the number of nets routed.
+    ``set_checkpointing`` keep working.  With ``fuse_layers`` the decoder layers also
+    take the fused forward of ``fuse_decoder_layers``.  Returns the number of nets routed.
     """
     n = 0
     for layer in model.model.layers:
@@ -301,4 +342,12 @@ def accelerate_locked_model(model) -> int:
         if not isinstance(net, DLRNet):
             mlp.dlrnet = DLRNet.adopt(net)
         n += 1
+    if fuse_layers:
+        # layers built by the reference carry its own wrapper class: same shape, re-wrapped so that the
+        # fused forward recognises them
+        for layer in model.model.layers:
+            mlp = getattr(layer, "mlp", None)
+            if mlp is not None and not isinstance(mlp, ResidualDLRNet) and _is_dlrnet_like(getattr(mlp, "dlrnet", None) or object()):
+                layer.mlp = ResidualDLRNet(mlp.dlrnet)
+        fuse_decoder_layers(model, True)
     return n

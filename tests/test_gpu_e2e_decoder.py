@@ -49,19 +49,35 @@ def test_locked_decoder_prefill_and_decode_logits():
         assert e_fast <= 1.25 * e_eager + 2e-3, (e_fast, e_eager)
         # near-ties of a random model flip on one ulp: most positions agree, not all
         assert (fast.logits.argmax(-1) == eager.logits.argmax(-1)).float().mean().item() >= 0.85
+        # the fused layer forward (attention output straight into the net, the net's output as the layer's
+        # output, dlr_lock/model.py:121-122's "- h" and the host layer's "+ h" never run): same gates, and no
+        # further from the fp32 model than the reference composition
+        assert D.fuse_decoder_layers(model, True) == 28
+        fused = model(ids, use_cache=True)
+        torch.cuda.synchronize()
+        D.ops.check_status()
+        assert _rel(fused.logits, eager.logits) <= 3e-2
+        assert _rel(fused.logits, want.logits) <= 1.25 * e_eager + 2e-3
+        pu = fused.past_key_values
 
         pe, pf = eager.past_key_values, fast.past_key_values
         tok = eager.logits[:, -1:].argmax(-1)
         for _ in range(3):
+            D.fuse_decoder_layers(model, False)
             D.set_fast_path(model, False)
             oe = model(tok, past_key_values=pe, use_cache=True)
             pe = oe.past_key_values
             D.set_fast_path(model, True)
+            D.fuse_decoder_layers(model, False)
             of = model(tok, past_key_values=pf, use_cache=True)
             pf = of.past_key_values
+            D.fuse_decoder_layers(model, True)
+            ou = model(tok, past_key_values=pu, use_cache=True)
+            pu = ou.past_key_values
             torch.cuda.synchronize()
             D.ops.check_status()
             assert _rel(of.logits, oe.logits) <= 3e-2
+            assert _rel(ou.logits, oe.logits) <= 3e-2
             tok = oe.logits[:, -1:].argmax(-1)
 
 

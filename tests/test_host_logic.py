@@ -167,3 +167,23 @@ def test_folded_cache_key_sees_an_edit_of_any_layer():
     net._folded = ("sentinel",)
     net.invalidate()
     assert net._folded is None
+
+
+def test_fused_decoder_layer_equals_the_reference_composition(tmp_path):
+    # dlr_lock/model.py:121-122 returns dlrnet(h) - h and the host layer adds h back; the fused layer
+    # forward returns dlrnet(h) directly.  In fp32 on the CPU the two agree to rounding.
+    path = _tiny_qwen3(str(tmp_path))
+    model = D.build_locked_model(path, rank=8, torch_dtype=torch.float32, alpha_init=0.3, verbose=False).eval()
+    ids = torch.randint(0, 128, (2, 7))
+    with torch.no_grad():
+        want = model(ids).logits
+        assert D.fuse_decoder_layers(model, True) == len(model.model.layers)
+        got = model(ids).logits
+        out = model(ids[:, :5], use_cache=True)                       # the KV cache path goes through the same forward
+        step = model(ids[:, 5:6], past_key_values=out.past_key_values, use_cache=True).logits
+        assert D.fuse_decoder_layers(model, False) == len(model.model.layers)
+        back = model(ids).logits
+        ref_step = model(ids[:, :6]).logits[:, -1:]
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-5)
+    assert torch.equal(back, want)
+    assert torch.allclose(step, ref_step, atol=1e-4, rtol=1e-4)
