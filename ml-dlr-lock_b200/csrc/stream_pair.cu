@@ -492,21 +492,16 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     const uint32_t buf = tl + kBufCol + b * 128u + uint32_t(32 * cq);   // this thread's 32 columns of the buffer
                     // ---- old values of the chunk: this thread's 64 bytes of its row, from the staging slot
                     DLP_TE(q, c, 0);
-                    // ---- everything this chunk needs, in one poll: lane 1 watches the buffer (dh has arrived; in
-                    // the pass over x: the V contraction of the chunk two before has read it, which dh_full implies
-                    // later), lane 2 the store slot, the other lanes the old values of the chunk
+                    // ---- what lands early, in one poll: lane 2 watches the store slot, the other lanes the old values
+                    // of the chunk; the old values are then fetched while dh is still on its way
                     {
                         uint32_t wbar = smem_u32(&bars->l_full[lp.st]), wpar = lp.ph;
-                        if (lane == 1) {
-                            wbar = q >= 0 ? smem_u32(&bars->dh_full[b]) : smem_u32(&bars->a_free[b]);
-                            wpar = q >= 0 ? ((b ? du1 : du0) & 1u) : (((n >> 1) & 1u) ^ 1u);
-                        } else if (lane == 2 && q >= 0) {
+                        if (lane == 2 && q >= 0) {
                             wbar = smem_u32(&bars->s_empty[sp.st]);
                             wpar = sp.ph ^ 1u;
                         }
                         if (!w.warp(wbar, wpar)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                     }
-                    tc_fence_after();
                     DLP_TE(q, c, 1);
                     uint32_t cur[16];
                     {
@@ -523,6 +518,11 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->l_free[lp.st]));
                     lp.step(kNLP);
+                    // ---- the buffer: dh has arrived (in the pass over x: the V contraction of the chunk two before has
+                    // read it, which dh_full implies later)
+                    if (!w.cta(q >= 0 ? smem_u32(&bars->dh_full[b]) : smem_u32(&bars->a_free[b]),
+                               q >= 0 ? ((b ? du1 : du0) & 1u) : (((n >> 1) & 1u) ^ 1u))) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    tc_fence_after();
                     if (q >= 0) {
                         if (b) ++du1; else ++du0;
                         DLP_TE(q, c, 2);
@@ -533,11 +533,11 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             if (PROF && (p.exp & 16)) { cur[j] ^= dv[2 * j] & dv[2 * j + 1]; continue; }
+                            // two columns at a time with the packed fp32 instructions (one add, one fma per pair)
                             const uint32_t hw = cur[j];
-                            const float f0 = bf16lo_to_f(hw) + __uint_as_float(dv[2 * j]);
-                            const float f1 = bf16hi_to_f(hw) + __uint_as_float(dv[2 * j + 1]);
-                            ssq0 = fmaf(f0, f0, ssq0);
-                            ssq1 = fmaf(f1, f1, ssq1);
+                            float f0, f1;
+                            add_f32x2(f0, f1, bf16lo_to_f(hw), bf16hi_to_f(hw), __uint_as_float(dv[2 * j]), __uint_as_float(dv[2 * j + 1]));
+                            fma_f32x2(ssq0, ssq1, f0, f1, f0, f1, ssq0, ssq1);
                             cur[j] = pack_bf16x2(f0, f1);
                         }
                     } else {
