@@ -21,7 +21,8 @@ from .model import (  # noqa: F401
     set_fast_path,
     write_config,
 )
-from . import harness, ops, packed, registry, sharding  # noqa: F401
+from . import evaluate, harness, ops, packed, registry, sharding  # noqa: F401
+from .evaluate import evaluate_ppl, synthetic_token_stream  # noqa: F401
 from .packed import PackedNet, load_packed_weights, pack_state_dict  # noqa: F401
 
 __version__ = "0.1.0"

@@ -66,8 +66,9 @@ def build_models(name: str = "Qwen3-0.6B", seed: int = 42, device="cuda"):
     torch.manual_seed(seed)
     swiglu = SwiGLU(d, d_ff).to(DTYPE).to(device)
     torch.manual_seed(seed)
-    us = [torch.randn(d, r) / math.sqrt(r * depth) for _ in range(depth)]
-    vs = [torch.randn(r, d) / math.sqrt(d) for _ in range(depth)]
+    u_scale, v_scale = 1.0 / math.sqrt(r * depth), 1.0 / math.sqrt(d)
+    us = [torch.randn(d, r) * u_scale for _ in range(depth)]
+    vs = [torch.randn(r, d) * v_scale for _ in range(depth)]
     net = DLRNet(d, r, depth, alpha_init=0.01)
     with torch.no_grad():
         for i in range(depth):

@@ -49,12 +49,36 @@ def build_case(DLRNet, d, r, L, M, seed, alpha, jitter):
     return net_bf, xb, y_bf, y_32, v_sum, u_sum
 
 
+def write_bench_twin(kref):
+    """Checksums of the benchmark twin of the net (kernels/reference.py:46-55: U drawn before V, alpha 0.01)
+    built as kernels/reference.py:94-102 does (seed 42), on the CPU, and its packed weights' checksums."""
+    out = {}
+    for name in ("Qwen3-0.6B",):
+        cfg = kref.MODEL_CONFIGS[name]
+        depth = kref.compute_depth(cfg["d"], cfg["d_ff"], cfg["r"])
+        torch.manual_seed(42)
+        net = kref.DLRNet(cfg["d"], cfg["r"], depth).to(kref.DTYPE)
+        packed = kref.pack_dlrnet_weights(net, device="cpu", premultiply=True)
+        out[name] = dict(depth=depth,
+                         u_sum=float(sum(u.double().sum() for u in net.Us)), v_sum=float(sum(v.double().sum() for v in net.Vs)),
+                         u0_first=float(net.Us[0].flatten()[0]), v0_first=float(net.Vs[0].flatten()[0]),
+                         alpha=float(net.alphas[0]),
+                         packed_Vs_sum=float(packed["Vs"].double().sum()), packed_Us_sum=float(packed["Us"].double().sum()),
+                         packed_Vs_shape=list(packed["Vs"].shape), packed_Us_shape=list(packed["Us"].shape))
+    with open(os.path.join(HERE, "bench_twin.json"), "w") as f:
+        json.dump(out, f, indent=1)
+
+
 def main():
     ref = sys.argv[1]
     sys.path.insert(0, ref)
     sys.path.insert(0, os.path.join(ref, "kernels"))
     from dlr_lock.model import DLRNet, compute_depth, dlrnet_param_count
     import reference as kref
+
+    write_bench_twin(kref)
+    if "--twin-only" in sys.argv:
+        return
 
     torch.set_num_threads(8)
     cases = [

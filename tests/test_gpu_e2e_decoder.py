@@ -81,6 +81,31 @@ def test_locked_decoder_prefill_and_decode_logits():
             tok = oe.logits[:, -1:].argmax(-1)
 
 
+def test_perplexity_with_the_library_matches_the_torch_loop():
+    # dlr_lock/eval_benchmarks.py:89-100 on a synthetic token stream (the stand-in of examples/smoke_test.py:40-48
+    # for the corpus): the locked model's perplexity with the CUDA library under its nets, with the fused layer
+    # forward on top, and with the torch layer loop agree within one percent
+    import dlr_lock_b200 as D
+    from transformers import AutoConfig
+
+    dev = "cuda:0"
+    torch.manual_seed(3)
+    cfg = AutoConfig.for_model("qwen3", vocab_size=4096, hidden_size=1024, intermediate_size=3072,
+                               num_hidden_layers=8, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                               max_position_embeddings=2048, tie_word_embeddings=True)
+    model = D.locked_model_from_config(cfg, rank=32, device=dev, alpha_init=0.01).eval()
+    ppl = {}
+    for name, fast, fused in (("torch_loop", False, False), ("library", True, False), ("library_fused", True, True)):
+        D.set_fast_path(model, fast)
+        D.fuse_decoder_layers(model, fused)
+        ppl[name] = D.evaluate_ppl(model, D.synthetic_token_stream(4096, 256, 4, seed=42), n_steps=4, device=dev)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert all(v == v and v > 1.0 for v in ppl.values()), ppl           # finite, and a loss was computed
+    assert abs(ppl["library"] / ppl["torch_loop"] - 1.0) <= 1e-2, ppl
+    assert abs(ppl["library_fused"] / ppl["torch_loop"] - 1.0) <= 1e-2, ppl
+
+
 def test_checkpoint_to_packed_weights(tmp_path):
     # layerNN.pt files written by save_dlrnet_weights, read straight into folded device stacks: the same
     # bits as the module computes from the same parameters, with and without the packed cache

@@ -583,3 +583,20 @@ def test_small_batch_exchange_is_exact_and_repeatable(D, d, r, L, M, monkeypatch
         torch.cuda.synchronize()
         D.ops.check_status()
         assert O.rel_l2(ys.cpu().float(), O.forward_fp32(xs, p).float()) <= 1e-2
+
+
+def test_cell_harness_gates_and_times_registry_cells(D):
+    # the bench-style harness (kernels/bench/bench_paper.py form): twin built with seed 42, reference = the torch
+    # module on the GPU, every cell gated on relative error and timed with the min-of-iterations protocol
+    from dlr_lock_b200 import harness
+    res = harness.sweep(["Qwen3-0.6B"], [8, 300], passes=2, n_iters=3, n_warmup=1, baselines=("swiglu", "orchestrated"))
+    rows = res["Qwen3-0.6B"]
+    for B in (8, 300):
+        cells = {c["kernel"]: c for c in rows[B]["cells"]}
+        assert rows[B]["SwiGLU"]["mean_us"] > 0
+        assert cells["cublas_graph_loop"]["status"] == "ok"
+        ours = [c for k, c in cells.items() if k.startswith("b200_")]
+        assert len(ours) == 1 and ours[0]["status"] == "ok", ours
+        assert ours[0]["rel_err"] <= harness.REL_ERR_TOL and ours[0]["update_err"] <= 0.35
+        assert ours[0]["mean_us"] > 0 and len(ours[0]["pass_mins_us"]) == 2 and "grid" in ours[0]["config"]
+    D.ops.check_status()

@@ -187,3 +187,46 @@ def test_fused_decoder_layer_equals_the_reference_composition(tmp_path):
     assert torch.allclose(got, want, atol=1e-5, rtol=1e-5)
     assert torch.equal(back, want)
     assert torch.allclose(step, ref_step, atol=1e-4, rtol=1e-4)
+
+
+def test_perplexity_consumer_on_cpu(tmp_path):
+    # dlr_lock/eval_benchmarks.py:89-100 on the synthetic stream: deterministic, finite, and equal for the same seed
+    path = _tiny_qwen3(str(tmp_path))
+    model = D.build_locked_model(path, rank=8, torch_dtype=torch.float32, alpha_init=0.1, verbose=False).eval()
+    a = D.evaluate_ppl(model, D.synthetic_token_stream(128, 16, 2, seed=7), n_steps=3, device="cpu")
+    b = D.evaluate_ppl(model, D.synthetic_token_stream(128, 16, 2, seed=7), n_steps=3, device="cpu")
+    assert a == b and 1.0 < a < 1e4
+    s = D.synthetic_token_stream(128, 16, 2, seed=7)
+    x = next(s)
+    assert x.shape == (2, 16) and x.dtype == torch.long and int(x.max()) < 128
+    with pytest.raises(ValueError):
+        D.synthetic_token_stream(128, 100000, 2)
+
+
+def test_bench_harness_twin_packer_and_cell_gate():
+    # the benchmark twin and packer against checksums written from the reference's own kernels/reference.py
+    # (tests/golden/bench_twin.json), and the ok / WRONG gate of the cell harness on the CPU
+    import json
+    import os
+    from conftest import GOLDEN
+    from dlr_lock_b200 import harness
+    with open(os.path.join(GOLDEN, "bench_twin.json")) as f:
+        want = json.load(f)["Qwen3-0.6B"]
+    swiglu, net, cfg = harness.build_models("Qwen3-0.6B", seed=42, device="cpu")
+    assert cfg["depth"] == want["depth"] == 141 and abs(float(net.alphas[0]) - want["alpha"]) < 1e-3
+    assert abs(float(sum(u.double().sum() for u in net.Us)) - want["u_sum"]) < 1e-6
+    assert abs(float(sum(v.double().sum() for v in net.Vs)) - want["v_sum"]) < 1e-6
+    assert float(net.Us[0].flatten()[0]) == want["u0_first"] and float(net.Vs[0].flatten()[0]) == want["v0_first"]
+    packed = harness.pack_dlrnet_weights(net, premultiply=True)
+    assert list(packed["Vs"].shape) == want["packed_Vs_shape"] and list(packed["Us"].shape) == want["packed_Us_shape"]
+    assert abs(float(packed["Vs"].double().sum()) - want["packed_Vs_sum"]) < 1e-9
+    assert abs(float(packed["Us"].double().sum()) - want["packed_Us_sum"]) < 1e-9
+    assert packed["premultiplied"] and packed["L"] == 141 and packed["D"] == 1024 and packed["R"] == 32
+    assert swiglu.gate_proj.weight.shape == (3072, 1024)
+    # gate: an identity "kernel" passes the total-error gate of the reference's harness and is exposed by the
+    # update error; a kernel that returns noise is WRONG
+    x = torch.randn(4, 1024).to(torch.bfloat16)
+    with torch.no_grad():
+        ref = net._forward_impl(x)
+    assert harness.rel_err(x, ref) <= harness.REL_ERR_TOL and harness.update_err(x, ref, x) > 0.99
+    assert harness.update_err(ref, ref, x) == 0.0
