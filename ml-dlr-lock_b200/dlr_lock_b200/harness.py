@@ -165,8 +165,11 @@ def build_run(entry: Dict, x: torch.Tensor, weights: Dict) -> Callable[[], torch
 
 
 def run_cell(kernel: str, run_factory: Callable[[], Callable[[], torch.Tensor]], x: torch.Tensor, ref: torch.Tensor,
-             baseline_us: Optional[float] = None, **measure_kw) -> Dict:
-    """Build, gate and time one cell (kernels/bench/bench_paper.py:126-147)."""
+             baseline_us: Optional[float] = None, ref32: Optional[torch.Tensor] = None, **measure_kw) -> Dict:
+    """Build, gate and time one cell (kernels/bench/bench_paper.py:126-147).  ``ref`` is the torch module's
+    bf16 output (the reference's gate); ``ref32`` its fp32 output on the same bf16 weights, against which the
+    update error is also reported: the bf16 module itself is most of the small update away from the fp32 one,
+    so a kernel that carries the activation in fp32 is judged against the latter."""
     try:
         run = run_factory()
         out = run()
@@ -177,6 +180,8 @@ def run_cell(kernel: str, run_factory: Callable[[], Callable[[], torch.Tensor]],
         stats = measure(run, **measure_kw)
         stats.update({"kernel": kernel, "status": "ok", "rel_err": err, "update_err": update_err(out, ref, x),
                       "ratio": stats["mean_us"] / baseline_us if baseline_us else None})
+        if ref32 is not None:
+            stats["update_err_fp32_ref"] = update_err(out, ref32.to(out.dtype), x)
         return stats
     except torch.cuda.OutOfMemoryError:
         free_all()
@@ -254,6 +259,8 @@ def sweep(models, batch_sizes, passes=N_PASSES, n_iters=N_ITERS, n_warmup=N_WARM
         weights = pack_dlrnet_weights(net, premultiply=True)
         results[model] = {}
         compiled = compiled_reduce_overhead(net) if "compile" in baselines else None
+        import copy
+        net32 = copy.deepcopy(net).float()
         for B in batch_sizes:
             free_all()
             row = {"cells": []}
@@ -263,6 +270,7 @@ def sweep(models, batch_sizes, passes=N_PASSES, n_iters=N_ITERS, n_warmup=N_WARM
                     net.fast = False
                     ref = net(x)
                     net.fast = True
+                    ref32 = net32._forward_impl(x.float())
                     sw = measure(lambda: swiglu(x), **kw) if "swiglu" in baselines else None
             except torch.cuda.OutOfMemoryError:
                 results[model][B] = {"status": "OOM building baseline"}
@@ -272,18 +280,18 @@ def sweep(models, batch_sizes, passes=N_PASSES, n_iters=N_ITERS, n_warmup=N_WARM
             base = sw["mean_us"] if sw else None
             if compiled is not None:
                 with torch.no_grad():
-                    row["cells"].append(run_cell("torch_compile_reduce_overhead", lambda: (lambda: compiled(x)), x, ref, base, **kw))
+                    row["cells"].append(run_cell("torch_compile_reduce_overhead", lambda: (lambda: compiled(x)), x, ref, base, ref32, **kw))
             if "orchestrated" in baselines:
                 def make():
                     g, hbuf = orchestrated_graph(x, weights)
                     return lambda: (g.replay(), hbuf)[1]
-                row["cells"].append(run_cell("cublas_graph_loop", make, x, ref, base, **kw))
+                row["cells"].append(run_cell("cublas_graph_loop", make, x, ref, base, ref32, **kw))
             entry = registry.describe(model, B, cfg["depth"])
-            row["cells"].append(run_cell(entry["kernel"], lambda: build_run(entry, x, weights), x, ref, base, **kw))
+            row["cells"].append(run_cell(entry["kernel"], lambda: build_run(entry, x, weights), x, ref, base, ref32, **kw))
             row["cells"][-1]["config"] = entry["config"]
             results[model][B] = row
-            del x, ref
-        del swiglu, net, weights, compiled
+            del x, ref, ref32
+        del swiglu, net, net32, weights, compiled
         free_all()
     return results
 

@@ -597,6 +597,9 @@ def test_cell_harness_gates_and_times_registry_cells(D):
         assert cells["cublas_graph_loop"]["status"] == "ok"
         ours = [c for k, c in cells.items() if k.startswith("b200_")]
         assert len(ours) == 1 and ours[0]["status"] == "ok", ours
-        assert ours[0]["rel_err"] <= harness.REL_ERR_TOL and ours[0]["update_err"] <= 0.35
+        # the update error against the bf16 module or against its fp32 twin, whichever activation format the
+        # kernel of the cell shares (a kernel that returns its input scores about 1 on both)
+        assert ours[0]["rel_err"] <= harness.REL_ERR_TOL
+        assert min(ours[0]["update_err"], ours[0]["update_err_fp32_ref"]) <= 0.35, ours[0]
         assert ours[0]["mean_us"] > 0 and len(ours[0]["pass_mins_us"]) == 2 and "grid" in ours[0]["config"]
     D.ops.check_status()
