@@ -413,7 +413,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
         // so that this warp never waits for a write in flight.
         if (lane == 0) {
             RingPos sp;
-            const uint64_t pol_h = l2_policy_evict_last();
+            const uint64_t pol_h = l2_policy_evict_last(), pol_out = l2_policy_evict_first();
             const bool hints = !(PROF && (p.exp & 32));
             unsigned int n = 0;              // chunks seen (all tiles, all passes): the producer counts the same way
             for (int t = 0; t < my_tiles && !err; ++t) {
@@ -429,9 +429,10 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                         DLP_T(5, q, c, 0);
                         if (m0 < p.M && !(PROF && (p.exp & 8))) {   // a CTA whose rows lie wholly past the batch stores nothing
                             const uint32_t src = sbuf_s + sp.st * kHBytesP;
-                            if (hints && q + 1 < p.L) {       // the last layer's output is not read again here
-                                tma_store_2d_hint(&tmY, col0 + c * kCWP, m0, src, pol_h);
-                                tma_store_2d_hint(&tmY, col0 + c * kCWP + 64, m0, src + 16384, pol_h);
+                            if (hints) {       // the last layer's output is not read again here: first to leave L2
+                                const uint64_t pol = q + 1 < p.L ? pol_h : pol_out;
+                                tma_store_2d_hint(&tmY, col0 + c * kCWP, m0, src, pol);
+                                tma_store_2d_hint(&tmY, col0 + c * kCWP + 64, m0, src + 16384, pol);
                             } else {
                                 tma_store_2d(&tmY, col0 + c * kCWP, m0, src);
                                 tma_store_2d(&tmY, col0 + c * kCWP + 64, m0, src + 16384);
@@ -747,7 +748,9 @@ int launch_pair(void* enc, const void* x, void* y, const void* Vp, const void* U
     p.prof = prof;
     p.trace_layer = L / 2;
     p.exp = 0;
-    if (const char* e = getenv("DLRB200_EXP")) p.exp = atoi(e);
+    if (prof) {
+        if (const char* e = getenv("DLRB200_EXP")) p.exp = atoi(e);
+    }
     const cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, tmX, tmY, tmV, tmU, p);
     return ce == cudaSuccess ? DLRB200_OK : DLRB200_ERR_CUDA;
 }
