@@ -65,6 +65,7 @@ extern "C" {
 #define DLRB200_PATH_CLUSTER 2 /* large batch: row tiles on CTA clusters, tcgen05 + tensor memory */
 #define DLRB200_PATH_CLUSTER_SMALL 3 /* small batch: one cluster per 2 rows, exchange in distributed shared memory */
 #define DLRB200_PATH_STREAMED 4 /* large batch: one CTA per 128-row tile, activations streamed through shared memory */
+#define DLRB200_PATH_STRIPED_CLUSTERS 6 /* small batch: width-striped CTAs in clusters of 8, exchange first inside the cluster, then through L2 */
 #define DLRB200_PATH_STREAMED_PAIRS 5 /* large batch: one CTA pair per 256-row tile (tcgen05 cta_group::2), activations streamed */
 
 typedef struct dlrb200_plan {

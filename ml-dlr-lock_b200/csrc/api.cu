@@ -7,6 +7,7 @@
 #include "cluster.h"
 #include "decode.h"
 #include "decode_cluster.h"
+#include "decode_tl.h"
 #include "stream.h"
 #include "stream_pair.h"
 
@@ -147,6 +148,44 @@ int striped_forward(const void* x, void* y, const void* Vp, const void* Up, int 
         }
     }
     return DLRB200_OK;
+}
+
+// The striped kernel with the two-level exchange (clusters of 8 first reduce among themselves): what small
+// batches beyond a few rows run on.  Measured at d = 4096, r = 128, L = 143 (us): see use_striped_clusters.
+int striped_tl_launch(const void* x, void* y, const void* Vp, const void* Up, int M, int d, int r, int L, float eps,
+                      void* workspace, int* status_dev, cudaStream_t stream, const DevInfo& di, dlrb200_plan* plan_only) {
+    const int dc = pick_stripe_cols(d, di.num_sms);
+    if (dc == 0 || !dlr::decode_tl_supported(d, r, dc)) return DLRB200_ERR_UNSUPPORTED_SHAPE;
+    dlr::DecodeTLLaunch a;
+    std::memset(&a, 0, sizeof(a));
+    a.d = d; a.r = r; a.L = L; a.dc = dc;
+    a.num_sms = di.num_sms;
+    a.smem_optin = di.smem_optin;
+    a.stream = stream;
+    a.p.M = M; a.p.d = d; a.p.L = L; a.p.eps = eps; a.p.inv_d = 1.0f / float(d);
+    a.p.status = status_dev;
+    a.p.spin_limit = spin_limit();
+    if (plan_only) return dlr::decode_tl_launch(a, plan_only);
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return DLRB200_ERR_CUDA;
+    int vbc, vbr, ubc, ubr, vsw, usw;
+    if (!dlr::decode_box_dims(r, dc, &vbc, &vbr, &ubc, &ubr, &vsw, &usw)) return DLRB200_ERR_UNSUPPORTED_SHAPE;
+    if (!dlr::encode_2d_bf16(reinterpret_cast<void*>(enc), &a.tmV, Vp, uint64_t(d), uint64_t(L) * r, vbc, vbr, vsw) ||
+        !dlr::encode_2d_bf16(reinterpret_cast<void*>(enc), &a.tmU, Up, uint64_t(r), uint64_t(L) * d, ubc, ubr, usw)) {
+        g_last_cuda_error = -1;
+        return DLRB200_ERR_CUDA;
+    }
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    const size_t clear = dlr::decode_tl_clear_bytes(M, r, L);
+    if (!cuda_ok(cudaMemsetAsync(ws, 0, clear, stream))) return DLRB200_ERR_CUDA;
+    a.p.x = static_cast<const __nv_bfloat16*>(x);
+    a.p.y = static_cast<__nv_bfloat16*>(y);
+    a.p.counter = reinterpret_cast<unsigned int*>(ws);
+    a.p.words = reinterpret_cast<unsigned long long*>(ws + 256);
+    a.p.pre = reinterpret_cast<float*>(ws + clear);
+    const int rc = dlr::decode_tl_launch(a, nullptr);
+    if (rc == DLRB200_ERR_CUDA) g_last_cuda_error = int(cudaGetLastError());
+    return rc;
 }
 
 __global__ void fold_v_kernel(const __nv_bfloat16* __restrict__ V, const __nv_bfloat16* __restrict__ gain,
@@ -320,6 +359,27 @@ bool use_cluster_small(int M, int d, int r) {
     return (d <= 1024 && M >= 2) || (d <= 2048 && M > 16);
 }
 
+// Small batches on the striped kernel with the two-level exchange (decode_tl.cu).  Measured on a B200, L about
+// 143, against the best of the other small-batch kernels (us): d = 4096, r = 128: 665 against 719 at 17 rows,
+// 754 / 853 at 32, 1012 / 1177 at 48, 1109 / 1184 at 64 (there the other is one padded 128-row tile on one
+// cluster), but 452 / 349 at one row and 598 / 554 at 16: its two hops through distributed shared memory cost
+// more than they save while the counted exchange of decode.cu applies.  d = 5120, r = 256: 785 / 933 at 16 rows,
+// 1117 / 1390 at 32 (more rows do not fit its shared memory).  d = 2048, r = 64: 585 / 794 at 32 rows, 735 / 759
+// at 48, 787 / 832 at 64, but 561 / 422 at 17 (cluster-small kernel).  d = 1024: never.
+// DLRB200_FORCE_PATH=6 forces it wherever it applies.
+bool use_striped_clusters(int M, int d, int r, int L, const DevInfo& di) {
+    const int forced = env_int("DLRB200_FORCE_PATH", 0);
+    if (M > 64) return false;
+    if (forced != 0 && forced != DLRB200_PATH_STRIPED_CLUSTERS) return false;
+    if (forced == 0) {
+        const int from = d >= 4096 ? (r >= 256 ? 16 : 17) : (d >= 2048 ? 29 : 65);
+        if (M < from) return false;
+    }
+    dlrb200_plan pl;
+    std::memset(&pl, 0, sizeof(pl));
+    return striped_tl_launch(nullptr, nullptr, nullptr, nullptr, M, d, r, L, 0.f, nullptr, nullptr, nullptr, di, &pl) == DLRB200_OK;
+}
+
 }  // namespace
 
 namespace dlr {
@@ -369,6 +429,8 @@ int dlrb200_last_cuda_error(void) { return g_last_cuda_error; }
 size_t dlrb200_workspace_bytes(int M, int d, int r, int L) {
     if (check_shape(M, d, r, L) != DLRB200_OK) return 0;
     size_t need = striped_workspace_bytes(r);
+    const size_t tl = dlr::decode_tl_workspace_bytes(M, r, L);
+    if (tl > need) need = tl;
     const size_t c = dlr::cluster_workspace_bytes(M, d, r, L);
     if (c > need) need = c;
     const size_t st = dlr::stream_workspace_bytes(M, d, r);
@@ -387,6 +449,12 @@ int dlrb200_query(int M, int d, int r, int L, dlrb200_plan* plan) {
     plan->workspace_bytes = dlrb200_workspace_bytes(M, d, r, L);
     if (use_pair_path(M, d, r, L, di)) return dlr::stream_pair_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
     if (use_stream_path(M, d, r, L, di)) return dlr::stream_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
+    if (use_striped_clusters(M, d, r, L, di)) {
+        const size_t ws = plan->workspace_bytes;
+        rc = striped_tl_launch(nullptr, nullptr, nullptr, nullptr, M, d, r, L, 0.f, nullptr, nullptr, nullptr, di, plan);
+        plan->workspace_bytes = ws;
+        return rc;
+    }
     if (use_cluster_path(M, d, r, L)) return dlr::cluster_plan(M, d, r, L, di.num_sms, di.smem_optin, plan);
     if (use_cluster_small(M, d, r)) return dlr::decode_cluster_plan(M, d, r, L, di.smem_optin, plan);
     const int dc = pick_stripe_cols(d, di.num_sms);
@@ -437,6 +505,8 @@ int dlrb200_forward(const void* x, void* y, const void* Vp, const void* Up, int 
         if (rc == DLRB200_ERR_CUDA) g_last_cuda_error = int(cudaGetLastError());
         return rc;
     }
+    if (use_striped_clusters(M, d, r, L, di))
+        return striped_tl_launch(x, y, Vp, Up, M, d, r, L, eps, workspace, status_dev, st, di, nullptr);
     if (use_cluster_path(M, d, r, L)) {
         EncodeTiledFn enc = encode_fn();
         if (!enc) return DLRB200_ERR_CUDA;

@@ -328,8 +328,11 @@ def test_streamed_path_is_chosen_where_it_is_faster_or_alone(D):
     assert q(16384, 2048, 64, 142).path == 5
     assert q(8192, 512, 64, 60).path == 2         # a cluster of one CTA has no exchange to lose time in
     assert q(4096, 5120, 256, 149).path == 4      # rank 256: one tensor-memory buffer, still streamed
-    assert q(40, 4096, 128, 143).path == 1
-    assert q(64, 4096, 128, 143).path == 2        # from about 52 rows a padded 128-row tile beats the striped kernel
+    assert q(16, 4096, 128, 143).path == 1        # counted exchange through L2
+    assert q(40, 4096, 128, 143).path == 6        # more rows: clusters of 8 reduce among themselves first
+    assert q(64, 4096, 128, 143).path == 6 and q(64, 4096, 128, 143).cluster == 8
+    assert q(64, 1024, 32, 141).path == 3 and q(20, 2048, 64, 142).path == 3 and q(40, 2048, 64, 142).path == 6
+    assert q(64, 5120, 256, 149).path == 1        # does not fit the two-level kernel's shared memory
 
 
 def test_streamed_path_several_tiles_per_cta_and_identity(D, monkeypatch):
@@ -603,3 +606,31 @@ def test_cell_harness_gates_and_times_registry_cells(D):
         assert min(ours[0]["update_err"], ours[0]["update_err_fp32_ref"]) <= 0.35, ours[0]
         assert ours[0]["mean_us"] > 0 and len(ours[0]["pass_mins_us"]) == 2 and "grid" in ours[0]["config"]
     D.ops.check_status()
+
+
+@pytest.mark.parametrize("d,r,L,M", [(4096, 128, 5, 3), (4096, 128, 5, 17), (4096, 128, 4, 64), (2048, 64, 6, 40),
+                                     (1024, 32, 7, 64), (5120, 256, 3, 20), (2048, 128, 3, 33), (4096, 128, 143, 48)])
+def test_two_level_small_batch_kernel(D, d, r, L, M, monkeypatch):
+    # striped grid in clusters of 8: reduce-scatter of the partial z and all-gather of s in distributed shared
+    # memory, cluster sums through counted words in L2.  Integer sums: two runs give the same bits.
+    monkeypatch.setenv("DLRB200_FORCE_PATH", "6")
+    dev = torch.device("cuda:0")
+    p, x = O.seeded_case(d, r, L, M, seed=d + L + M, alpha=0.05 if L > 50 else 1.0, gain_jitter=0.1)
+    plan = D.ops.query(M, d, r, L)
+    assert plan.path == 6 and plan.cluster == 8 and plan.grid % 8 == 0
+    Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
+    xd = x.to(dev)
+    y1 = D.ops.forward_folded(xd, Vf, Uf, p.eps)
+    y2 = D.ops.forward_folded(xd, Vf, Uf, p.eps)
+    torch.cuda.synchronize()
+    D.ops.check_status()
+    assert torch.equal(y1, y2)
+    want = O.forward_fp32(x, p)
+    assert O.rel_l2(y1.cpu(), want) <= 5e-3
+    assert O.rel_l2_update_q(y1.cpu(), want, x) <= (TOL_UPDATE_FP32H if L > 50 else 2e-2)
+    for scale in (1e-3, 1e3):               # partials are normalised by the running 1/rms: no dependence on the input's scale
+        xs = (x.float() * scale).to(torch.bfloat16)
+        ys = D.ops.forward_folded(xs.to(dev), Vf, Uf, p.eps)
+        torch.cuda.synchronize()
+        D.ops.check_status()
+        assert O.rel_l2(ys.cpu().float(), O.forward_fp32(xs, p).float()) <= 1e-2
