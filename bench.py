@@ -613,11 +613,11 @@ def main():
     ms_step = ms / args.steps
     value = world * M * 1e3 / ms_step
 
-    path_name = {1: "striped", 2: "cluster", 3: "cluster_small", 4: "streamed", 5: "streamed_pairs"}.get(plan.path, "?")
+    path_name = {1: "striped", 2: "cluster", 3: "cluster_small", 4: "streamed", 5: "streamed_pairs", 6: "striped_clusters"}.get(plan.path, "?")
     launches_per_step = plan.passes if plan.path == 1 else 1   # the striped path launches once per 64 rows
     kernel_ms = ms_step / launches_per_step
     timed_s = ms / 1e3
-    if plan.path in (1, 3):
+    if plan.path in (1, 3, 6):
         # small-batch kernels stream the weights once per launch: HBM-bound by design
         bytes_alg = 4.0 * L * d * r + 4.0 * min(M, 64) * d
         achieved = bytes_alg / (kernel_ms * 1e-3) / 1e9
@@ -655,7 +655,7 @@ def main():
     }
 
     # ---- the same step for at least two seconds: what the kernel sustains under the power cap
-    if not args.no_extras and plan.path not in (1, 3):
+    if not args.no_extras and plan.path not in (1, 3, 6):
         n_long = int(math.ceil(2200.0 / ms_step))
         s2 = ClockSampler(local)
         s2.start()
