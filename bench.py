@@ -632,8 +632,9 @@ def main():
         alg_bytes = 4.0 * L * d * r + 4.0 * M * d
         if args.workload == "cfg3" and M == 8192 and plan.path == 5:
             # one ncu capture of this very launch (profiles/streamed_pairs_kernel_cfg3_M8192.md)
-            traffic, note = 1.057e9 + 1.574e9, ("measured: dram__bytes_read + dram__bytes_write of one captured launch of this "
-                                                "configuration; the activations (134 MB through L2 per layer) do not stay in L2 entirely")
+            traffic, note = 0.707e9 + 0.924e9, ("measured: dram__bytes_read + dram__bytes_write of one captured launch of this "
+                                                "configuration (a second capture: 1.06 + 1.57 GB); the activations (134 MB through "
+                                                "L2 per layer) do not stay in L2 entirely")
         else:
             traffic, note = plan.passes * 4.0 * L * d * r + 4.0 * M * d, "not captured at this size: waves x weights + activations"
         roofline = {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
