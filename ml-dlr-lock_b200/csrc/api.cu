@@ -28,6 +28,7 @@ struct DevInfo {
     int num_sms = 0;
     int smem_optin = 0;
     int cc_major = 0;
+    int l2_bytes = 0;
     bool ok = false;
 };
 
@@ -44,7 +45,8 @@ int device_info(DevInfo* out) {
     if (!d.ok) {
         if (!cuda_ok(cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev)) ||
             !cuda_ok(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) ||
-            !cuda_ok(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev)))
+            !cuda_ok(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) ||
+            !cuda_ok(cudaDeviceGetAttribute(&d.l2_bytes, cudaDevAttrL2CacheSize, dev)))
             return DLRB200_ERR_CUDA;
         d.ok = true;
     }
@@ -296,6 +298,13 @@ int large_batch_path(int M, int d, int r, int L, const DevInfo& di) {
             const double t_pass = pl.cluster >= 4 ? 6.8 : (pl.cluster == 2 ? 5.5 : 2.5);
             double t = double(pl.passes) * (L + 1) * (double(d / 128 / pl.cluster) * (r >= 128 ? 1.26 : 1.15) + t_pass);
             if (pl.cluster == 1 && pl.grid > 100 && 4.0 * L * d * r > 100e6) t *= 1.3;
+            // every layer rewrites the rows in flight in place: once they outgrow L2 (beside the weight stream)
+            // each layer's traffic goes to DRAM (measured at d = 4096: 12288 / 16384 / 18944 rows in flight
+            // cost 1.11 / 1.24 / 1.41 times the estimate)
+            if (di.l2_bytes > 0) {
+                const double ratio = double(pl.grid / pl.cluster) * 128.0 * d * 2.0 / double(di.l2_bytes);
+                if (ratio > 0.62) t *= 1.0 + 0.65 * (ratio - 0.62);
+            }
             if (t < best) { best = t; path = DLRB200_PATH_STREAMED; }
         }
     }
@@ -304,9 +313,9 @@ int large_batch_path(int M, int d, int r, int L, const DevInfo& di) {
         if (dlr::stream_pair_plan(M, d, r, L, di.num_sms, di.smem_optin, &pl) == DLRB200_OK) {
             const int pp = pl.cluster / 2;
             // (measured only where the pairs cover most of the GPU: not taken for smaller grids)
-            if ((pp == 2 || r == 64) && pl.grid >= 96) {
-                const double t = double(pl.passes) * (L + 1) *
-                                 (double(d / 128 / pp) * (r >= 128 ? 1.09 : 0.80) + (pp == 2 ? 4.4 : 2.5));
+            if (pp == 4 || ((pp == 2 || r == 64) && pl.grid >= 96)) {
+                const double pause = (r >= 128 ? 3.4 : 2.0) + (pp == 4 ? 2.8 : (pp == 2 ? 1.0 : 0.0));
+                const double t = double(pl.passes) * (L + 1) * (double(d / 128 / pp) * (r >= 128 ? 1.09 : 0.80) + pause);
                 if (t < best) { best = t; path = DLRB200_PATH_STREAMED_PAIRS; }
             }
         }

@@ -29,17 +29,20 @@
 // second CTA signal the leader's barriers with remote arrives; the leader's
 // tcgen05.commit signals the barriers of both CTAs.
 //
-// Two pairs per cluster (when there are too few 256-row tiles to fill the
-// GPU): pair 0 takes the first half of the chunks, pair 1 the second; once per
-// layer each CTA sends its partial z (bf16) and partial sums of squares to the
-// CTA that holds the same rows in the other pair, straight into its shared
-// memory with st.async (bytes counted on the receiver's barrier: no fences, no
-// trip through global memory), and both add the two partials.
+// Two or four pairs per cluster (when there are too few 256-row tiles to fill
+// the GPU) split the width: pair i takes the i-th part of the chunks; once per
+// layer the CTAs that hold the same rows add up their partial z and partial
+// sums of squares in one or two exchange steps (partner: pair i ^ 1, then pair
+// i ^ 2).  A step sends the running sum (rounded to bf16) straight into the
+// partner's shared memory with st.async (bytes counted on the receiver's
+// barrier: no fences, no trip through global memory), and both sides add own
+// (rounded alike) + received: every CTA ends with the same bits.
 //
 // All waits are bounded; a wait that gives up raises an abort flag, records a
 // status word and every role drains and leaves.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "ptx.cuh"
 #include "stream_pair.h"
@@ -97,8 +100,9 @@ struct PBars {
     uint64_t a_free[2];          // commit, both CTAs: the V contraction has read the chunk, the buffer is free
     uint64_t z_full;             // commit, both CTAs
     uint64_t s_ready;            // leader: 32 epilogue warps
-    uint64_t xchg_bar;           // two pairs: the other pair's message has arrived (bytes)
-    uint64_t xack_bar;           // two pairs: the 16 epilogue warps of the other pair have read what this CTA sent
+    uint64_t xchg_bar[2];        // per exchange step: the partner's message has arrived (bytes)
+    uint64_t xack_bar[2];        // per exchange step: the 16 epilogue warps of that step's partner have read their receive
+                                 // buffer, this CTA may send its next message of that step
     uint64_t ssq_bar;            // the 16 epilogue warps have published their quarters of the sums of squares
     uint64_t drain[2];           // all tensor-core work of an MMA warp is complete (waited for before leaving)
     uint32_t tmem_slot;
@@ -110,7 +114,7 @@ static_assert(sizeof(PBars) <= 512, "barrier block");
 struct PParams {
     int M, d, L;
     int nch;                  // chunks per row: d / 128
-    int pp;                   // pairs per cluster (1 or 2), each with nch / pp of the chunks
+    int pp;                   // pairs per cluster (1, 2 or 4), each with nch / pp of the chunks
     int num_tiles;            // 256-row tiles
     float eps, inv_d;
     int* status;
@@ -158,7 +162,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
     const int hf = int(crank & 1u);                 // 0: leader of the pair
     const int pi = int(crank >> 1);                 // pair within the cluster
     const uint32_t lead = crank & ~1u;              // cluster rank of this pair's leader
-    const uint32_t partner = crank ^ 2u;            // the CTA with the same rows in the other pair (pp == 2)
+    const int nsteps = pp == 4 ? 2 : (pp == 2 ? 1 : 0);   // exchange steps per layer; step s: partner = pair pi ^ (1 << s)
     const uint16_t pair_mask = uint16_t(3u << lead);
 
     if (threadIdx.x == 0) {
@@ -183,8 +187,10 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
         }
         mbar_init(smem_u32(&bars->z_full), 1);
         mbar_init(smem_u32(&bars->s_ready), 2 * kEpiWarpsP);
-        mbar_init(smem_u32(&bars->xchg_bar), 1);
-        mbar_init(smem_u32(&bars->xack_bar), kEpiWarpsP);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars->xchg_bar[b]), 1);
+            mbar_init(smem_u32(&bars->xack_bar[b]), kEpiWarpsP);
+        }
         mbar_init(smem_u32(&bars->ssq_bar), kEpiWarpsP);
         mbar_init(smem_u32(&bars->drain[0]), 1);
         mbar_init(smem_u32(&bars->drain[1]), 1);
@@ -471,11 +477,6 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             if (hf) mbar_arrive_remote_light(bar);
             else mbar_arrive(bar);
         };
-        // the other pair's receive buffer, barrier and acknowledge barrier
-        const uint32_t p_recv = pp > 1 ? mapa(smem_u32(recv), partner) : 0u;
-        const uint32_t p_recv_q = pp > 1 ? mapa(smem_u32(recv_q), partner) : 0u;
-        const uint32_t p_xchg = pp > 1 ? mapa(smem_u32(&bars->xchg_bar), partner) : 0u;
-        const uint32_t p_xack = pp > 1 ? mapa(smem_u32(&bars->xack_bar), partner) : 0u;
 
         RingPos lp, sp;
         const int trole = (warp == 4 && lane == 0) ? 6 : ((warp == 19 && lane == 0) ? 7 : -1);
@@ -587,20 +588,33 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     if constexpr (NZ == 32) tmem_ld32(tl + kZCol + uint32_t(cq * NZ), zv);
                     else tmem_ld16(tl + kZCol + uint32_t(cq * NZ), zv);
                     tmem_wait_ld();
-                    if (pp > 1) {
-                        // The two pairs hold partial z over their halves of the width.  Each CTA sends its partial
-                        // (rounded to bf16) and its partial sums of squares to the CTA with the same rows in the
-                        // other pair, and both add own (rounded alike) + received: the same s on both sides.
-                        // The receiver's buffer is free once it has acknowledged the message of the layer before.
-                        if (c_z > 0 && !w.cluster(smem_u32(&bars->xack_bar), (c_z - 1u) & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                        if (et == 0) mbar_arrive_expect_tx(smem_u32(&bars->xchg_bar), C::RECV_BYTES);
+                    // The pairs hold partial z over their parts of the width.  In step s each CTA sends its running
+                    // sum (rounded to bf16) and its sum of squares so far to the CTA with the same rows in pair
+                    // pi ^ (1 << s), and both add own (rounded alike) + received: the same s on all sides.  All steps
+                    // of a CTA receive into one buffer: a message is sent once the receiver has read the one before.
+                    for (int step = 0; step < nsteps; ++step) {
+                        const uint32_t partner = crank ^ (2u << step);
+                        if (step == 0) {
+                            // the first partner acknowledged the last message of the layer before
+                            if (c_z > 0 && !w.cluster(smem_u32(&bars->xack_bar[0]), (c_z - 1u) & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        } else {
+                            // this CTA has read the message of the step before: the partner of this step may send; and
+                            // that partner must have read its own
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive_remote_light(mapa(smem_u32(&bars->xack_bar[step]), partner));
+                            if (!w.cluster(smem_u32(&bars->xack_bar[step]), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        }
+                        const uint32_t p_recv = mapa(smem_u32(recv), partner);
+                        const uint32_t p_recv_q = mapa(smem_u32(recv_q), partner);
+                        const uint32_t p_xchg = mapa(smem_u32(&bars->xchg_bar[step]), partner);
+                        if (et == 0) mbar_arrive_expect_tx(smem_u32(&bars->xchg_bar[step]), C::RECV_BYTES);
 #pragma unroll
                         for (int k = 0; k < C::NZW; ++k) {
                             const float* f = reinterpret_cast<const float*>(&zv[8 * k]);
                             const uint32_t o0 = pack_bf16x2(f[0], f[1]), o1 = pack_bf16x2(f[2], f[3]);
                             const uint32_t o2 = pack_bf16x2(f[4], f[5]), o3 = pack_bf16x2(f[6], f[7]);
                             st_async_v4(p_recv + uint32_t((k * kEpiThreadsP + et) * 16), o0, o1, o2, o3, p_xchg);
-                            // own partial, rounded like the one that was sent
+                            // own running sum, rounded like the one that was sent
                             zv[8 * k] = o0 << 16; zv[8 * k + 1] = o0 & 0xffff0000u;
                             zv[8 * k + 2] = o1 << 16; zv[8 * k + 3] = o1 & 0xffff0000u;
                             zv[8 * k + 4] = o2 << 16; zv[8 * k + 5] = o2 & 0xffff0000u;
@@ -608,7 +622,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                         }
                         st_async_b32(p_recv_q + uint32_t(et * 4), __float_as_uint(ssq), p_xchg);
                         DLP_TE(q, 24, 2);
-                        if (!w.cluster(smem_u32(&bars->xchg_bar), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                        if (!w.cluster(smem_u32(&bars->xchg_bar[step]), c_z & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                         DLP_TE(q, 24, 3);
                         ssq += recv_q[et];
 #pragma unroll
@@ -621,6 +635,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                             f[6] += bf16lo_to_f(v.w); f[7] += bf16hi_to_f(v.w);
                         }
                     }
+                    if (err) break;
                     ssqx[cq * kRowsP + er] = ssq;              // index et: the word this thread's received partial came in
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->ssq_bar));
@@ -629,10 +644,10 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     const float tot = (ssqx[er] + ssqx[kRowsP + er]) + (ssqx[2 * kRowsP + er] + ssqx[3 * kRowsP + er]);
                     const float rstd = rsqrtf(tot * p.inv_d + p.eps);
                     DLP_TE(q, 24, 4);
-                    if (pp > 1) {
-                        // the message and the words shared with it have been read: the sender may overwrite them
+                    if (nsteps > 0) {
+                        // the last message and the words shared with it have been read: the first partner may send again
                         __syncwarp();
-                        if (lane == 0) mbar_arrive_remote_light(p_xack);
+                        if (lane == 0) mbar_arrive_remote_light(mapa(smem_u32(&bars->xack_bar[0]), crank ^ 2u));
                     }
                     uint32_t sv[NZ / 2];
 #pragma unroll
@@ -670,15 +685,35 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
     }
 }
 
-// Pairs per cluster: two when one pair per 256-row tile would leave most of the GPU idle and every pair still
-// gets at least four chunks (the store warp reports a chunk as stored two chunks late and the producer runs up
-// to three chunks ahead).
-int pick_pairs(int num_tiles, int nch, int num_sms) {
+// Shape of a launch: pairs per cluster (1, 2 or 4: they split the width) and clusters in the grid.  For each
+// number of pairs that fits, estimated time = rounds x (chunks per pair x time per chunk + the pause at the end
+// of a layer, which grows with the exchange steps), where the clusters of a round are as many as can be resident
+// and no more than keep the rows in flight inside L2: every layer rewrites its tile in place, and once the tiles
+// of a round outgrow L2 each layer's traffic goes to DRAM (measured at d = 4096: 16384 rows at once 8.2 ms, in
+// two rounds of 8448 rows 6.6 ms).  Every pair keeps at least four chunks (the store warp reports a chunk as
+// stored two chunks late and the producer runs up to three chunks ahead).
+struct PairShape { int pp, clusters; };
+PairShape pick_shape(int num_tiles, int d, int r, const int (&max_clusters)[3], size_t l2_bytes) {
     int forced = 0;
     if (const char* e = getenv("DLRB200_PAIR_SPLIT")) forced = atoi(e);
-    if (forced == 1) return 1;
-    if (nch % 2 == 0 && nch / 2 >= 4 && (forced == 2 || num_tiles * 4 <= num_sms)) return 2;
-    return 1;
+    const int nch = d / kCWP;
+    const double t_chunk = r == 128 ? 1.09 : 0.80;
+    const size_t tile_bytes = size_t(2 * kRowsP) * d * 2;
+    int fit = int(double(l2_bytes) * 0.62 / double(tile_bytes));      // tiles whose rows stay in L2 beside the weight stream
+    if (fit < 1) fit = 1;
+    PairShape best{0, 0};
+    double best_t = 1e30;
+    for (int pp = 1, i = 0; pp <= 4; pp *= 2, ++i) {
+        if (forced && pp != forced) continue;
+        if (nch % pp || nch / pp < 4 || max_clusters[i] < 1) continue;
+        int clusters = max_clusters[i] < fit ? max_clusters[i] : fit;
+        if (clusters > num_tiles) clusters = num_tiles;
+        const int rounds = (num_tiles + clusters - 1) / clusters;
+        const double pause = (r == 128 ? 3.4 : 2.0) + (pp == 4 ? 2.8 : (pp == 2 ? 1.0 : 0.0));
+        const double t = rounds * ((nch / pp) * t_chunk + pause);
+        if (t < best_t) { best_t = t; best = PairShape{pp, clusters}; }
+    }
+    return best;
 }
 
 template <int R>
@@ -688,35 +723,51 @@ int launch_pair(void* enc, const void* x, void* y, const void* Vp, const void* U
     using C = PCfg<R>;
     if (C::SMEM_BYTES > smem_optin) return DLRB200_ERR_OCCUPANCY;
     const int num_tiles = (M + 2 * kRowsP - 1) / (2 * kRowsP);
-    int pp = pick_pairs(num_tiles, d / kCWP, num_sms);
     auto kern = prof ? dlr_stream_pair_kernel<R, true> : dlr_stream_pair_kernel<R, false>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-        return DLRB200_ERR_CUDA;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cudaLaunchAttribute attr[1];
     cfg.blockDim = dim3(kThreadsP);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = stream;
-    int clusters = 0;
-    for (;;) {
-        const int cs = 2 * pp;
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = cs;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        cfg.gridDim = dim3(cs * (num_sms / cs));
-        int max_clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess) return DLRB200_ERR_CUDA;
-        if (max_clusters < 1) return DLRB200_ERR_OCCUPANCY;
-        // two pairs per cluster only while every tile is resident at once; one pair per cluster walks the tiles
-        // in waves if it must
-        if (pp == 2 && max_clusters < num_tiles) { pp = 1; continue; }
-        clusters = num_tiles < max_clusters ? num_tiles : max_clusters;
-        break;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // per process (one device per process) and kernel: shared-memory opt-in, clusters of 2, 4 and 8 CTAs that can
+    // be resident at once, size of L2
+    struct DeviceFacts { bool known; int max_clusters[3]; size_t l2_bytes; };
+    static DeviceFacts facts[2] = {{false, {0, 0, 0}, 0}, {false, {0, 0, 0}, 0}};
+    static std::mutex facts_mutex;
+    DeviceFacts f;
+    {
+        std::lock_guard<std::mutex> lock(facts_mutex);
+        DeviceFacts& slot = facts[prof ? 1 : 0];
+        if (!slot.known) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+                return DLRB200_ERR_CUDA;
+            for (int i = 0; i < 3; ++i) {
+                const int cs = 2 << i;
+                attr[0].val.clusterDim.x = cs;
+                cfg.gridDim = dim3(cs * (num_sms / cs));
+                int mc = 0;
+                if (cudaOccupancyMaxActiveClusters(&mc, kern, &cfg) != cudaSuccess) mc = 0;
+                slot.max_clusters[i] = mc;
+            }
+            int dev = 0, l2 = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev) != cudaSuccess)
+                return DLRB200_ERR_CUDA;
+            slot.l2_bytes = size_t(l2);
+            slot.known = true;
+        }
+        f = slot;
     }
+    const PairShape sh = pick_shape(num_tiles, d, R, f.max_clusters, f.l2_bytes);
+    if (sh.pp < 1) return DLRB200_ERR_OCCUPANCY;
+    const int pp = sh.pp, clusters = sh.clusters;
+    attr[0].val.clusterDim.x = 2 * pp;
     const int grid = clusters * 2 * pp;
     cfg.gridDim = dim3(grid);
     if (plan_only) {

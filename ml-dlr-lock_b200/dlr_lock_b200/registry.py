@@ -18,13 +18,15 @@ MODEL_CONFIGS = {  # kernels/reference.py:18-23
 _CALLABLE = "dlr_lock_b200.ops.forward_xvu"
 
 PATH_NAMES = {1: "b200_striped", 2: "b200_cluster", 3: "b200_cluster_small", 4: "b200_streamed",
-              5: "b200_streamed_pairs"}
+              5: "b200_streamed_pairs", 6: "b200_striped_clusters"}
 PATH_CONFIGS = {
     1: "width-striped cooperative grid, TMA weight ring, one exchange per layer through L2",
     2: "128-row tiles on clusters of d/512 CTAs, activations resident in tensor memory, tcgen05",
     3: "one cluster of d/256 CTAs per two rows, exchange in distributed shared memory",
     4: "128-row tiles, one cluster of 1/2/4 CTAs each, activations streamed through shared and tensor memory, tcgen05",
     5: "256-row tiles on CTA pairs (tcgen05 cta_group::2), activations streamed, exchange in distributed shared memory",
+    6: "width-striped cooperative grid in clusters of 8: reduction inside a cluster in distributed shared memory, "
+       "cluster sums through counted words in L2",
 }
 
 
@@ -37,9 +39,15 @@ def _entries(name):
     d, r = MODEL_CONFIGS[name]["d"], MODEL_CONFIGS[name]["r"]
     small = 3 if d <= 1024 else 1
     big = 2 if r < 64 or d <= 2048 else 4
-    return [
-        _entry(1, 64, small, "Small batch: one launch walks all layers, one exchange per layer."),
-        _entry(65, 131072, big, "Large batch: row tiles on tensor cores, one launch for all layers."),
+    rows = [_entry(1, 64, small, "Small batch: one launch walks all layers, one exchange per layer.")]
+    if d >= 2048:
+        split = 17 if d >= 4096 else 29          # from where the two-level exchange is the faster one
+        rows = [_entry(1, split - 1, small, "Small batch: one launch walks all layers, one exchange per layer."),
+                _entry(split, 64, 6, "Small batch, more rows: the exchange in two levels.")]
+    big_pairs = 5 if r in (64, 128) else big
+    return rows + [
+        _entry(65, 4095, big, "Large batch: row tiles on tensor cores, one launch for all layers."),
+        _entry(4096, 131072, big_pairs, "Largest batches: 256-row tiles on CTA pairs where the shape allows."),
     ]
 
 

@@ -43,8 +43,10 @@ CASES = [
     ("cfg3", 16, STRIPED, 1, 64),
     ("cfg3", 64, None, None, None),
     ("cfg3", 1024, None, None, None),
+    ("cfg3", 2048, STREAMED_PAIRS, 8, 64),
     ("cfg3", 4096, STREAMED, None, None),
     ("cfg3", 8192, STREAMED_PAIRS, 4, 128),
+    ("cfg3", 16384, STREAMED_PAIRS, 4, None),
     ("cfg4", 1, STRIPED, 1, 80),
     ("cfg4", 64, STRIPED, 1, 80),
     ("cfg4", 4096, STREAMED, None, None),

@@ -135,3 +135,22 @@ def test_checkpoint_to_packed_weights(tmp_path):
     D.ops.check_status()
     with pytest.raises(ValueError):
         D.pack_state_dict({"Vs.0": torch.zeros(4, 8)}, dev)
+    # an fp32 checkpoint, as the reference's distillation writes it (dlr_lock/distill_logits.py:196-200): the
+    # serving module holds it in bf16 (alpha included) before folding, and so does the packed path
+    net32 = D.DLRNet(512, 64, 5, alpha_init=0.0123456)
+    with torch.no_grad():
+        for w in net32.rms_w:
+            w.add_(0.1 * torch.randn(512))
+    ckpt32 = str(tmp_path / "ckpt32")
+    os.makedirs(ckpt32)
+    torch.save(net32.state_dict(), os.path.join(ckpt32, "layer00.pt"))
+    served = D.DLRNet(512, 64, 5)
+    served.load_state_dict(torch.load(os.path.join(ckpt32, "layer00.pt"), weights_only=True))
+    served = served.to(dev).to(torch.bfloat16).eval()
+    (packed32,) = D.load_packed_weights(ckpt32, dev, n_layers=1, eps=1e-6)
+    Vp, Up = served.folded_weights()
+    assert torch.equal(packed32.Vp, Vp) and torch.equal(packed32.Up, Up)
+    # the caller's epsilon applies on a cache hit, not the one stored with the packed stacks
+    D.load_packed_weights(ckpt32, dev, n_layers=1, eps=1e-6, write_cache=True)
+    (hit,) = D.load_packed_weights(ckpt32, dev, n_layers=1, eps=1e-5)
+    assert hit.eps == 1e-5 and torch.equal(hit.Vp, Vp)

@@ -317,8 +317,13 @@ def test_streamed_path_is_chosen_where_it_is_faster_or_alone(D):
     assert q(6144, 4096, 128, 143).path == 5
     assert q(4096, 4096, 128, 143).path == 4      # too few 256-row tiles for the pairs: 128-row tiles, clusters of 4
     assert q(4096, 4096, 128, 143).cluster == 4
-    assert q(16384, 4096, 128, 143).path == 4     # one CTA per tile, no exchange at all
-    assert q(19200, 4096, 128, 143).path == 2     # two streamed waves lose again
+    # more rows than stay in L2 between two layers: the pairs walk them in rounds of as many tiles as fit
+    assert q(16384, 4096, 128, 143).path == 5 and q(16384, 4096, 128, 143).cluster == 4
+    assert q(16384, 4096, 128, 143).passes == 2
+    assert q(32768, 4096, 128, 143).path == 5
+    # too few tiles for two pairs each to fill the GPU: four pairs per cluster split the width four ways
+    assert q(2048, 4096, 128, 143).path == 5 and q(2048, 4096, 128, 143).cluster == 8
+    assert q(3840, 4096, 128, 143).path == 5 and q(3840, 4096, 128, 143).grid == 120
     assert q(4096, 8192, 128, 40).path == 4       # wider than a cluster of 8 can hold
     assert q(8192, 1536, 64, 40).path == 5        # not a multiple of the cluster kernel's 512-column stripe
     assert q(2048, 1536, 64, 40).path == 4
@@ -362,16 +367,18 @@ def test_streamed_path_several_tiles_per_cta_and_identity(D, monkeypatch):
 @pytest.mark.parametrize("d,r,L,M,split", [(512, 128, 3, 256, 0), (512, 128, 2, 100, 0), (1024, 128, 5, 300, 1),
                                            (1024, 128, 5, 300, 2), (2048, 64, 7, 1000, 2), (1536, 64, 4, 257, 0),
                                            (4096, 128, 3, 129, 0), (640, 128, 3, 65, 0), (1024, 128, 1, 65, 0),
-                                           (2048, 128, 2, 90, 1), (2048, 64, 3, 513, 0), (512, 64, 2, 130, 0)])
+                                           (2048, 128, 2, 90, 1), (2048, 64, 3, 513, 0), (512, 64, 2, 130, 0),
+                                           (2048, 64, 7, 1000, 4), (4096, 128, 3, 700, 4), (2048, 128, 4, 300, 4),
+                                           (2048, 64, 3, 30000, 4), (1024, 128, 3, 40000, 2)])
 def test_pair_path_shapes(D, d, r, L, M, split, monkeypatch):
     # ragged row counts (the second CTA of the last pair partly or wholly past the batch), odd chunk counts,
-    # one and two pairs per cluster
+    # one, two and four pairs per cluster (none, one and two exchange steps per layer), several rounds
     monkeypatch.setenv("DLRB200_FORCE_PATH", "5")
     if split:
         monkeypatch.setenv("DLRB200_PAIR_SPLIT", str(split))
     p, x = O.seeded_case(d, r, L, M, seed=d + r + M, alpha=1.0, gain_jitter=0.1)
     plan = D.ops.query(M, d, r, L)
-    assert plan.path == 5 and plan.cluster in (2, 4) and plan.rows_per_pass == 256
+    assert plan.path == 5 and plan.cluster in (2, 4, 8) and plan.rows_per_pass == 256
     if split:
         assert plan.cluster == 2 * split
     y, Vf, Uf = _run(D, p, x)
@@ -383,7 +390,7 @@ def test_pair_path_shapes(D, d, r, L, M, split, monkeypatch):
 
 
 @pytest.mark.parametrize("name", ["cfg2_d2048_r64", "cfg3_d4096_r128", "toy_d512_r64_stress"])
-@pytest.mark.parametrize("split", [1, 2])
+@pytest.mark.parametrize("split", [1, 2, 4])
 def test_pair_path_against_reference_fixtures(D, name, split, monkeypatch):
     g = load_golden(name)
     m = g["meta"]
@@ -392,8 +399,8 @@ def test_pair_path_against_reference_fixtures(D, name, split, monkeypatch):
     xx = x.repeat(reps, 1)
     monkeypatch.setenv("DLRB200_FORCE_PATH", "5")
     monkeypatch.setenv("DLRB200_PAIR_SPLIT", str(split))
-    if split == 2 and m["d"] < 1024:
-        pytest.skip("two pairs per cluster need at least eight chunks")
+    if m["d"] // 128 // split < 4:
+        pytest.skip("every pair needs at least four chunks")
     assert D.ops.query(xx.shape[0], m["d"], m["r"], m["L"]).path == 5
     y, Vf, Uf = _run(D, p, xx)
     for k in range(reps):                        # rows are independent: every copy gives the fixture's answer
@@ -440,9 +447,12 @@ def test_pair_path_several_tiles_per_cluster_identity_and_graph_replay(D, monkey
     assert torch.equal(out, y)
 
 
-def test_pair_path_reports_a_timeout_instead_of_hanging(D, monkeypatch):
+@pytest.mark.parametrize("split", [0, 4])
+def test_pair_path_reports_a_timeout_instead_of_hanging(D, split, monkeypatch):
     monkeypatch.setenv("DLRB200_FORCE_PATH", "5")
-    p, x = O.seeded_case(1024, 128, 4, 600, seed=9, alpha=1.0, gain_jitter=0.1)
+    if split:
+        monkeypatch.setenv("DLRB200_PAIR_SPLIT", str(split))
+    p, x = O.seeded_case(2048, 128, 4, 600, seed=9, alpha=1.0, gain_jitter=0.1)
     dev = torch.device("cuda:0")
     Vf, Uf = D.ops.fold_weights(p.V.to(dev), p.U.to(dev), p.w.to(dev), p.alpha.to(dev))
     monkeypatch.setenv("DLRB200_SPIN_LIMIT", "4")
