@@ -759,13 +759,19 @@ def main():
                         "algorithmic_GBps": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "tokens_per_s": m / (lo * 1e-6)})
         line["decode"] = dec
         pre = []
-        for m in (1024, 4096):
-            if m >= M:
+        for m in (1024, 2048, 3840, 4096, 16384):
+            if m == M:
                 continue
-            xm, ym = xs[0][:m].contiguous(), torch.empty(m, d, device=dev, dtype=torch.bfloat16)
+            if m < M:
+                xm = xs[0][:m].contiguous()
+            else:       # more rows than stay in L2 between two layers: walked in rounds
+                xm = torch.cat([xs[0]] * ((m + M - 1) // M))[:m].contiguous()
+            ym = torch.empty(m, d, device=dev, dtype=torch.bfloat16)
             lo, med = min_latency_us(lambda: ops.forward_folded(xm, Vp, Up, out=ym), iters=10, warmup=3)
-            pre.append({"M": m, "path": ops.query(m, d, r, L).path, "min_us": lo, "tokens_per_s": m / (lo * 1e-6),
-                        "TFLOPs": 4.0 * L * m * d * r / (lo * 1e-6) / 1e12})
+            pl = ops.query(m, d, r, L)
+            pre.append({"M": m, "path": pl.path, "grid": pl.grid, "cluster": pl.cluster, "rounds": pl.passes, "min_us": lo,
+                        "tokens_per_s": m / (lo * 1e-6), "TFLOPs": 4.0 * L * m * d * r / (lo * 1e-6) / 1e12})
+            del xm, ym
         line["prefill_other"] = pre
         ops.check_status()
         line["same_box"] = same_box_comparisons(dev, xs[0], Vp, Up, d, r, L, seed, args.workload, M)
