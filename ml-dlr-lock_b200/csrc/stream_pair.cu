@@ -1,7 +1,7 @@
 // Large-batch ("prefill") DLR-Net forward, streamed path on CTA pairs: two CTAs
 // walk one 256-row tile of the batch through all L layers with tensor-core
 // instructions of M = 256 (tcgen05 cta_group::2); a cluster holds one pair, or
-// two pairs that split the width.
+// two or four pairs that split the width.
 //
 // Same data flow as the one-CTA streamed kernel (stream.cu): rows are
 // independent (dlr_lock/model.py:96-100 acts on each token alone), the
@@ -23,9 +23,9 @@
 // each SM's port halve; nothing is multicast, each CTA loads its own half with
 // a plain TMA load whose bytes are counted on the leader's barrier.
 //
-// Roles per CTA (384 threads): TMA producer, U-MMA issuer and V-MMA issuer
+// Roles per CTA (640 threads): TMA producer, U-MMA issuer and V-MMA issuer
 // (these two work in the leader, the even-ranked CTA of the pair, only), store
-// warp (owns tensor memory), 8 epilogue warps.  The epilogue warps of the
+// warp (owns tensor memory), 16 epilogue warps.  The epilogue warps of the
 // second CTA signal the leader's barriers with remote arrives; the leader's
 // tcgen05.commit signals the barriers of both CTAs.
 //
@@ -78,7 +78,7 @@ struct PCfg {
     static constexpr int V_BYTES = 2 * V_TILE_BYTES;
     static constexpr int NU = R == 128 ? 2 : 4;
     static constexpr int NV = R == 128 ? 2 : 4;
-    // message of one thread to the other pair: its R/4 columns of z as bf16 (NZW words of 16 bytes) and its
+    // message of one thread to a partner pair: its R/4 columns of z as bf16 (NZW words of 16 bytes) and its
     // partial sum of squares (4 bytes)
     static constexpr int NZ = R / 4;
     static constexpr int NZW = NZ / 8;
