@@ -91,11 +91,15 @@ struct PCfg {
 struct PBars {
     uint64_t u_full[kMaxWP], u_empty[kMaxWP];   // full: in the leader, bytes of both CTAs; empty: commit, both CTAs
     uint64_t v_full[kMaxWP], v_empty[kMaxWP];
-    uint64_t l_full[kNLP];       // old chunk has landed (TMA bytes)
     uint64_t l_free[kNLP];       // the 16 epilogue warps have it in registers
     uint64_t s_written[kNSP];    // the 16 epilogue warps have written the new chunk
-    uint64_t s_empty[kNSP];      // the store warp's bulk copy has read it
-    uint64_t dh_full[2];         // commit, both CTAs: dh of the chunk is in the buffer
+    // The one barrier an epilogue thread waits for per chunk (a look at an mbarrier costs a few hundred cycles even
+    // when its phase is complete, and the epilogue is on the loop that bounds the time per chunk).  Chunk n uses
+    // buffer, load slot and store slot n & 1, and barrier [n & 1] collects three arrivals: the commit of the U
+    // contraction (both CTAs; in the pass over x an empty commit once the buffer is free), the producer's arrival
+    // that carries the byte count of the old values, and the store warp's arrival when the bulk store of the chunk
+    // two before has read the store slot.
+    uint64_t dh_full[2];
     uint64_t a_ready[2];         // leader: the 32 epilogue warps have put the updated chunk (bf16) into the buffer
     uint64_t a_free[2];          // commit, both CTAs: the V contraction has read the chunk, the buffer is free
     uint64_t z_full;             // commit, both CTAs
@@ -173,15 +177,13 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             mbar_init(smem_u32(&bars->v_empty[s]), 1);
         }
         for (int s = 0; s < kNLP; ++s) {
-            mbar_init(smem_u32(&bars->l_full[s]), 1);
             mbar_init(smem_u32(&bars->l_free[s]), kEpiWarpsP);
         }
         for (int s = 0; s < kNSP; ++s) {
             mbar_init(smem_u32(&bars->s_written[s]), kEpiWarpsP);
-            mbar_init(smem_u32(&bars->s_empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&bars->dh_full[b]), 1);
+            mbar_init(smem_u32(&bars->dh_full[b]), 3);
             mbar_init(smem_u32(&bars->a_ready[b]), 2 * kEpiWarpsP);
             mbar_init(smem_u32(&bars->a_free[b]), 1);
         }
@@ -248,11 +250,13 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             const bool hints = !(PROF && (p.exp & 32));
             while ((nu < total_w || nv < total_w || nh < total_h) && !err) {
                 bool did = false;
+                // The epilogue threads wait for one barrier per chunk (a look at an mbarrier costs them a few hundred
+                // cycles): the bytes of the old values are counted on the chunk's own barrier (slot n & 1 = buffer n & 1).
                 // pass >= 1 reads what this CTA stored one pass (nch chunks) earlier
                 if (nh < total_h && (hq < 1 || *stored + unsigned(nch) > unsigned(nh)) &&
                     mbar_test(smem_u32(&bars->l_free[hp.st]), hp.ph ^ 1u)) {
                     if (hq >= 1) asm volatile("fence.proxy.async.global;" ::: "memory");
-                    const uint32_t bar = smem_u32(&bars->l_full[hp.st]);
+                    const uint32_t bar = smem_u32(&bars->dh_full[hp.st]);
                     const uint32_t dst = lbuf_s + hp.st * kHBytesP;
                     const CUtensorMap* src = hq >= 1 ? &tmY : &tmX;
                     const int m0 = (cl + ht * ncl) * 2 * kRowsP + hf * kRowsP;
@@ -319,7 +323,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                 // copies requested before giving up still land in shared memory: wait for them (the weight copies of
                 // both CTAs are counted in the leader, which the second CTA outlasts through the cluster barrier)
                 for (int i = 0; i < kNLP; ++i)
-                    if (hph[i] >= 0) mbar_wait(smem_u32(&bars->l_full[i]), uint32_t(hph[i]), kDrainPolls);
+                    if (hph[i] >= 0) mbar_wait(smem_u32(&bars->dh_full[i]), uint32_t(hph[i]), kDrainPolls);
                 if (hf == 0) {
                     for (int i = 0; i < int(NU); ++i)
                         if (uph[i] >= 0) mbar_wait_cluster(smem_u32(&bars->u_full[i]), uint32_t(uph[i]), kDrainPolls);
@@ -337,7 +341,13 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             uint32_t n = 0;
             uint32_t c_s = 0;
             for (int t = 0; t < my_tiles && !err; ++t) {
-                n += uint32_t(nch);          // the pass over x goes through the buffers too (chunk n: buffer n & 1)
+                // the pass over x goes through the buffers too (chunk n: buffer n & 1): nothing to multiply, but the
+                // chunk's barrier gets its commit (which arrives at once) when the buffer is free
+                for (int c = 0; c < nch && !err; ++c, ++n) {
+                    const uint32_t b = n & 1u;
+                    if (!w.cta(smem_u32(&bars->a_free[b]), ((n >> 1) & 1u) ^ 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    umma_commit2_mask(smem_u32(&bars->dh_full[b]), pair_mask);
+                }
                 for (int q = 0; q < p.L && !err; ++q) {
                     err_layer = q;
                     DLP_T(3, q, 0, 7);
@@ -422,18 +432,19 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
             const uint64_t pol_h = l2_policy_evict_last(), pol_out = l2_policy_evict_first();
             const bool hints = !(PROF && (p.exp & 32));
             unsigned int n = 0;              // chunks seen (all tiles, all passes): the producer counts the same way
+            // the store slots of the first two chunks are free from the start
+            mbar_arrive(smem_u32(&bars->dh_full[0]));
+            mbar_arrive(smem_u32(&bars->dh_full[1]));
             for (int t = 0; t < my_tiles && !err; ++t) {
                 const int m0 = (cl + t * ncl) * 2 * kRowsP + hf * kRowsP;
-                // the pass over x stores nothing; it is also the point where the tile before is fully stored
-                bulk_wait_group<0>();
-                n += unsigned(nch);
-                *stored = n;
-                for (int q = 0; q < p.L && !err; ++q) {
+                // (the pass over x stores nothing but walks the slots like the others: chunk n uses slot n & 1, as it
+                // uses buffer n & 1)
+                for (int q = -1; q < p.L && !err; ++q) {
                     err_layer = q;
                     for (int c = 0; c < nch; ++c, ++n) {
                         if (!w.cta(smem_u32(&bars->s_written[sp.st]), sp.ph)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
                         DLP_T(5, q, c, 0);
-                        if (m0 < p.M && !(PROF && (p.exp & 8))) {   // a CTA whose rows lie wholly past the batch stores nothing
+                        if (q >= 0 && m0 < p.M && !(PROF && (p.exp & 8))) {   // a CTA whose rows lie wholly past the batch stores nothing
                             const uint32_t src = sbuf_s + sp.st * kHBytesP;
                             if (hints) {       // the last layer's output is not read again here: first to leave L2
                                 const uint64_t pol = q + 1 < p.L ? pol_h : pol_out;
@@ -447,7 +458,8 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                         bulk_commit_group();
                         bulk_wait_group_read<0>();
                         DLP_T(5, q, c, 1);
-                        mbar_arrive(smem_u32(&bars->s_empty[sp.st]));
+                        // the slot is free for the chunk after next: one of the three arrivals its barrier waits for
+                        mbar_arrive(smem_u32(&bars->dh_full[sp.st]));
                         sp.step(kNSP);
                         bulk_wait_group<2>();            // every group but the last two is complete
                         if (n + 1u > *stored + 2u) *stored = n + 1u - 2u;
@@ -468,7 +480,6 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
         const int et = int(threadIdx.x) - 128;            // = cq * 128 + er
         const uint32_t tl = tmem_base + (uint32_t(32 * q4) << 16);
         uint32_t n = 0;                      // chunks seen (all passes): phase of the A operand's barriers
-        uint32_t du0 = 0, du1 = 0;           // times each buffer has received a dh: phase of its dh_full barrier
         uint32_t c_z = 0;
         // barriers of the leader that this warp signals: its own if this CTA leads, else through the cluster window
         const uint32_t l_a_ready = hf ? mapa(smem_u32(&bars->a_ready[0]), lead) : smem_u32(&bars->a_ready[0]);
@@ -494,16 +505,10 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     const uint32_t buf = tl + kBufCol + b * 128u + uint32_t(32 * cq);   // this thread's 32 columns of the buffer
                     // ---- old values of the chunk: this thread's 64 bytes of its row, from the staging slot
                     DLP_TE(q, c, 0);
-                    // ---- what lands early, in one poll: lane 2 watches the store slot, the other lanes the old values
-                    // of the chunk; the old values are then fetched while dh is still on its way
-                    {
-                        uint32_t wbar = smem_u32(&bars->l_full[lp.st]), wpar = lp.ph;
-                        if (lane == 2 && q >= 0) {
-                            wbar = smem_u32(&bars->s_empty[sp.st]);
-                            wpar = sp.ph ^ 1u;
-                        }
-                        if (!w.warp(wbar, wpar)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                    }
+                    // ---- the one wait of a chunk: dh is in the buffer (in the pass over x: the buffer is free), the old
+                    // values of the chunk have landed in their slot and the store slot is free
+                    if (!w.cta(smem_u32(&bars->dh_full[b]), (n >> 1) & 1u)) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
+                    tc_fence_after();
                     DLP_TE(q, c, 1);
                     uint32_t cur[16];
                     {
@@ -516,21 +521,15 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                             cur[4 * j] = hv.x; cur[4 * j + 1] = hv.y; cur[4 * j + 2] = hv.z; cur[4 * j + 3] = hv.w;
                         }
                     }
-                    // the old values are in registers: the slot can take the next chunk at once
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bars->l_free[lp.st]));
-                    lp.step(kNLP);
-                    // ---- the buffer: dh has arrived (in the pass over x: the V contraction of the chunk two before has
-                    // read it, which dh_full implies later)
-                    if (!w.cta(q >= 0 ? smem_u32(&bars->dh_full[b]) : smem_u32(&bars->a_free[b]),
-                               q >= 0 ? ((b ? du1 : du0) & 1u) : (((n >> 1) & 1u) ^ 1u))) { err = DLRB200_ERR_TIMEOUT_BARRIER; break; }
-                    tc_fence_after();
                     if (q >= 0) {
-                        if (b) ++du1; else ++du0;
                         DLP_TE(q, c, 2);
                         uint32_t dv[32];
                         tmem_ld32(buf, dv);
                         tmem_wait_ld();
+                        // the old values are in registers (the loads above have returned by now): the slot can take the
+                        // next chunk
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->l_free[lp.st]));
                         DLP_TE(q, c, 3);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
@@ -544,6 +543,8 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                         }
                     } else {
                         // pass over x: the chunk goes to the tensor core as it is
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->l_free[lp.st]));
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const float f0 = bf16lo_to_f(cur[j]), f1 = bf16hi_to_f(cur[j]);
@@ -551,6 +552,7 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                             ssq1 = fmaf(f1, f1, ssq1);
                         }
                     }
+                    lp.step(kNLP);
                     // ---- the chunk (bf16) becomes the A operand of the next layer's contraction, over this thread's own
                     // columns of dh: first, because the tensor core waits for it
                     DLP_TE(q, c, 4);
@@ -561,13 +563,15 @@ dlr_stream_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_con
                     if (lane == 0) arrive_lead(l_a_ready + 8u * b);
                     DLP_TE(q, c, 6);
                     // ---- new values into a store slot: the store warp copies the slot out
-                    if (q >= 0) {
-                        uint8_t* rowp = sbuf + sp.st * kHBytesP + row_off;
+                    {
+                        if (q >= 0) {
+                            uint8_t* rowp = sbuf + sp.st * kHBytesP + row_off;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (!(PROF && (p.exp & 4))) *reinterpret_cast<uint4*>(rowp + (((piece0 + uint32_t(j)) ^ x7) << 4)) =
-                                make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
-                        fence_async_smem();
+                            for (int j = 0; j < 4; ++j)
+                                if (!(PROF && (p.exp & 4))) *reinterpret_cast<uint4*>(rowp + (((piece0 + uint32_t(j)) ^ x7) << 4)) =
+                                    make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
+                            fence_async_smem();
+                        }
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&bars->s_written[sp.st]));
                         sp.step(kNSP);
